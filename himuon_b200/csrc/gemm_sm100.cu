@@ -1,0 +1,363 @@
+// Persistent batched bf16 GEMM for sm_100a:  C[b] = alpha * op(A[b]) * op(B[b]) + beta * Aux[b]
+//
+//   * operands are staged by TMA (128-byte swizzle, no multicast) into a shared-memory ring,
+//   * one elected thread issues tcgen05.mma (M=128, N=BN, K=16) into TMEM accumulators,
+//   * four epilogue warps read TMEM with tcgen05.ld, apply the epilogue and store,
+//   * two TMEM accumulators (2 x BN columns) let the epilogue of tile i overlap the MMAs of tile i+1.
+//
+// Either operand may be K-major (reduction dim contiguous) or MN-major (M/N contiguous),
+// so forward (x W^T), dgrad (dy W) and wgrad (dy^T x) all run without a transpose pass.
+// This one kernel replaces the reference's three Triton GEMM kernels
+// (src/himuon/triton_kernels/XXT.py:12-75, ba_plus_cAA.py:12-89, fused_bmm_add.py:12-96)
+// and the cuBLAS calls behind F.linear / torch.addmm.
+#include "himuon.h"
+#include "sm100_common.cuh"
+#include "tma_host.h"
+
+namespace himuon {
+
+__device__ int g_status_word = 0;
+
+struct GemmDev {
+  void* C;
+  const void* aux;
+  int M, N, K, batch;
+  long long ldc, ldaux, strideC, strideAux;
+  float alpha, beta;
+  int out_fp32;     // 1: C/aux are fp32, 0: bf16
+  int round_acc;    // 1: round alpha*acc to bf16 before adding beta*aux
+  int tiles_m, tiles_n, kblocks;
+  int* status;
+};
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(256, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmDev p) {
+  constexpr uint32_t A_BYTES = BM * BK * 2;
+  constexpr uint32_t B_BYTES = BN * BK * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t CHUNK_BYTES = BK * 128;  // one 64-wide MN chunk of an MN-major tile
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align_up_1024(smem_raw);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 2) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int total_tiles = tiles_per_batch * p.batch;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int b = tile / tiles_per_batch;
+        const int r = tile - b * tiles_per_batch;
+        const int mt = r % p.tiles_m;
+        const int nt = r / p.tiles_m;
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          uint8_t* sA = smem + stage * STAGE_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
+          if (!A_MN) {
+            tma_load_3d(sA, &tmA, &full[stage], kb * BK, mt * BM, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_3d(sA + j * CHUNK_BYTES, &tmA, &full[stage], mt * BM + j * 64, kb * BK, b);
+          }
+          if (!B_MN) {
+            tma_load_3d(sB, &tmB, &full[stage], kb * BK, nt * BN, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sB + j * CHUNK_BYTES, &tmB, &full[stage], nt * BN + j * 64, kb * BK, b);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag, p.status, 2)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 2)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t b_base = a_base + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? umma_smem_desc(a_base + k * 2048, CHUNK_BYTES, 1024)
+                                        : umma_smem_desc(a_base + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + k * 2048, CHUNK_BYTES, 1024)
+                                        : umma_smem_desc(b_base + k * 32, 16, 1024);
+            umma_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue (warps 4..7 -> TMEM lanes 0..127)
+    const int ew = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int b = tile / tiles_per_batch;
+      const int r = tile - b * tiles_per_batch;
+      const int mt = r % p.tiles_m;
+      const int nt = r / p.tiles_m;
+      if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, p.status, 3)) break;
+      tc_fence_after();
+      const int row = mt * BM + ew * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      const long long c_off = static_cast<long long>(b) * p.strideC + static_cast<long long>(row) * p.ldc;
+      const long long x_off = static_cast<long long>(b) * p.strideAux + static_cast<long long>(row) * p.ldaux;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col = nt * BN + c0;
+        if (col >= p.N) break;  // uniform over the warp
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld32(t_row + c0, v);
+        tmem_ld_wait();
+        const bool full_vec = (col + 32 <= p.N);
+        if (!row_ok) {
+          // rows past M hold padding; nothing to store
+        } else if (p.out_fp32) {
+          float* cp = reinterpret_cast<float*>(p.C) + c_off + col;
+          const float* xp = p.aux ? reinterpret_cast<const float*>(p.aux) + x_off + col : nullptr;
+          if (full_vec && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0) &&
+              (!xp || (reinterpret_cast<uintptr_t>(xp) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o;
+              o.x = p.alpha * __uint_as_float(v[j + 0]);
+              o.y = p.alpha * __uint_as_float(v[j + 1]);
+              o.z = p.alpha * __uint_as_float(v[j + 2]);
+              o.w = p.alpha * __uint_as_float(v[j + 3]);
+              if (xp) {
+                const float4 e = *reinterpret_cast<const float4*>(xp + j);
+                o.x += p.beta * e.x; o.y += p.beta * e.y; o.z += p.beta * e.z; o.w += p.beta * e.w;
+              }
+              *reinterpret_cast<float4*>(cp + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col + j < p.N) {
+                float o = p.alpha * __uint_as_float(v[j]);
+                if (xp) o += p.beta * xp[j];
+                cp[j] = o;
+              }
+            }
+          }
+        } else {
+          __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + col;
+          const __nv_bfloat16* xp = p.aux ? reinterpret_cast<const __nv_bfloat16*>(p.aux) + x_off + col : nullptr;
+          if (full_vec && ((reinterpret_cast<uintptr_t>(cp) & 15) == 0) &&
+              (!xp || (reinterpret_cast<uintptr_t>(xp) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float f[8];
+#pragma unroll
+              for (int t = 0; t < 8; ++t) f[t] = p.alpha * __uint_as_float(v[j + t]);
+              if (xp) {
+                const uint4 e = *reinterpret_cast<const uint4*>(xp + j);
+                const uint32_t ew4[4] = {e.x, e.y, e.z, e.w};
+                if (p.round_acc) {
+#pragma unroll
+                  for (int t = 0; t < 8; ++t) f[t] = round_bf16(f[t]);
+                }
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  f[2 * t] += p.beta * bf16_lo(ew4[t]);
+                  f[2 * t + 1] += p.beta * bf16_hi(ew4[t]);
+                }
+              }
+              uint4 o;
+              o.x = pack_bf16x2(f[0], f[1]);
+              o.y = pack_bf16x2(f[2], f[3]);
+              o.z = pack_bf16x2(f[4], f[5]);
+              o.w = pack_bf16x2(f[6], f[7]);
+              *reinterpret_cast<uint4*>(cp + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col + j < p.N) {
+                float o = p.alpha * __uint_as_float(v[j]);
+                if (xp) {
+                  if (p.round_acc) o = round_bf16(o);
+                  o += p.beta * __bfloat162float(xp[j]);
+                }
+                cp[j] = __float2bfloat16_rn(o);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static void launch_gemm(const GemmArgs& a, cudaStream_t stream) {
+  constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * 2;
+  constexpr size_t SMEM = 1024 + STAGES * STAGE_BYTES + 256;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM));
+    attr_done = true;
+  }
+  // A: K-major storage (M rows x K) or MN-major storage (K rows x M).
+  uint64_t dimsA[3], strA[2], dimsB[3], strB[2];
+  uint32_t boxA[3], boxB[3];
+  if (!A_MN) { dimsA[0] = a.K; dimsA[1] = a.M; boxA[0] = BK; boxA[1] = BM; }
+  else       { dimsA[0] = a.M; dimsA[1] = a.K; boxA[0] = 64; boxA[1] = BK; }
+  dimsA[2] = a.batch; boxA[2] = 1;
+  strA[0] = static_cast<uint64_t>(a.lda) * 2;
+  strA[1] = a.batch > 1 ? static_cast<uint64_t>(a.strideA) * 2 : strA[0] * dimsA[1];
+  if (!B_MN) { dimsB[0] = a.K; dimsB[1] = a.N; boxB[0] = BK; boxB[1] = BN; }
+  else       { dimsB[0] = a.N; dimsB[1] = a.K; boxB[0] = 64; boxB[1] = BK; }
+  dimsB[2] = a.batch; boxB[2] = 1;
+  strB[0] = static_cast<uint64_t>(a.ldb) * 2;
+  strB[1] = a.batch > 1 ? static_cast<uint64_t>(a.strideB) * 2 : strB[0] * dimsB[1];
+  CUtensorMap tmA = make_tmap(a.A, 3, dimsA, strA, boxA, 2, true);
+  CUtensorMap tmB = make_tmap(a.B, 3, dimsB, strB, boxB, 2, true);
+
+  GemmDev p;
+  p.C = a.C; p.aux = a.aux;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
+  p.ldc = a.ldc; p.ldaux = a.ldaux; p.strideC = a.strideC; p.strideAux = a.strideAux;
+  p.alpha = a.alpha; p.beta = a.beta; p.out_fp32 = a.out_fp32; p.round_acc = a.round_acc;
+  p.tiles_m = (a.M + BM - 1) / BM;
+  p.tiles_n = (a.N + BN - 1) / BN;
+  p.kblocks = (a.K + BK - 1) / BK;
+  p.status = status_word_ptr();
+  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batch;
+  int sms = a.max_ctas > 0 ? a.max_ctas : num_sms();
+  const int grid = static_cast<int>(total < sms ? total : sms);
+  kern<<<grid, 256, SMEM, stream>>>(tmA, tmB, p);
+}
+
+int num_sms() {
+  static int sms[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (sms[dev] == 0) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+  return sms[dev];
+}
+
+void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0 || a.batch <= 0) return;
+  if (a.K <= 0) throw std::runtime_error("himuon gemm: K must be positive");
+  // Narrow outputs use the 128-wide tile (more tiles, deeper ring); wide ones the 256-wide tile.
+  const long long tiles256 = static_cast<long long>((a.M + BM - 1) / BM) * ((a.N + 255) / 256) * a.batch;
+  const bool bn128 = a.N <= 128 || tiles256 < num_sms();
+  const int sel = (a.a_mn ? 2 : 0) | (a.b_mn ? 1 : 0);
+  if (bn128) {
+    switch (sel) {
+      case 0: launch_gemm<128, 6, false, false>(a, stream); break;
+      case 1: launch_gemm<128, 6, false, true>(a, stream); break;
+      case 2: launch_gemm<128, 6, true, false>(a, stream); break;
+      default: launch_gemm<128, 6, true, true>(a, stream); break;
+    }
+  } else {
+    switch (sel) {
+      case 0: launch_gemm<256, 4, false, false>(a, stream); break;
+      case 1: launch_gemm<256, 4, false, true>(a, stream); break;
+      case 2: launch_gemm<256, 4, true, false>(a, stream); break;
+      default: launch_gemm<256, 4, true, true>(a, stream); break;
+    }
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) throw std::runtime_error(std::string("himuon gemm launch failed: ") + cudaGetErrorString(e));
+}
+
+int* status_word_ptr() {
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess)
+      throw std::runtime_error("himuon: cannot resolve the device status word");
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  return ptrs[dev];
+}
+
+int read_status_word(bool reset) {
+  int v = 0;
+  cudaMemcpy(&v, status_word_ptr(), sizeof(int), cudaMemcpyDeviceToHost);
+  if (reset && v != 0) cudaMemset(status_word_ptr(), 0, sizeof(int));
+  return v;
+}
+
+}  // namespace himuon

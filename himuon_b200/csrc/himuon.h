@@ -1,0 +1,138 @@
+// Host-side C++ interface of the sm_100a kernel library.  Every launcher takes raw
+// device pointers and a stream; nothing here depends on PyTorch.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <stdexcept>
+#include <string>
+
+namespace himuon {
+
+// ---------------------------------------------------------------- runtime helpers
+int num_sms();
+int* status_word_ptr();              // device address of the bounded-wait status word
+int read_status_word(bool reset);    // synchronous read (0 = healthy)
+
+// ---------------------------------------------------------------- GEMM
+// C[b] = alpha * op(A[b]) * op(B[b]) + beta * aux[b], bf16 operands, fp32 accumulate.
+// a_mn = false: A stored (M x K) with K contiguous;  true: stored (K x M) with M contiguous.
+// b_mn = false: B stored (N x K) with K contiguous;  true: stored (K x N) with N contiguous.
+// lda/ldb are the element strides between stored rows; all leading dims and batch strides
+// must be multiples of 8 elements (TMA needs 16-byte strides).
+struct GemmArgs {
+  const void* A = nullptr;
+  const void* B = nullptr;
+  void* C = nullptr;
+  const void* aux = nullptr;
+  int M = 0, N = 0, K = 0, batch = 1;
+  long long lda = 0, ldb = 0, ldc = 0, ldaux = 0;
+  long long strideA = 0, strideB = 0, strideC = 0, strideAux = 0;
+  bool a_mn = false, b_mn = false;
+  float alpha = 1.f, beta = 0.f;
+  int out_fp32 = 0;
+  int round_acc = 0;
+  int max_ctas = 0;   // 0 = one CTA per SM
+};
+void gemm_bf16(const GemmArgs& args, cudaStream_t stream);
+
+// ---------------------------------------------------------------- optimizer kernels
+constexpr int kMaxSrc = 8;
+
+// One matrix whose gradient is folded into momentum and written out as NS tiles.
+struct MomTileEntry {
+  const void* grad[kMaxSrc];  // gradient replicas to sum (this rank's plus peers'), same dtype
+  void* mom;                  // momentum buffer, same dtype as the gradient
+  long long tile_base;        // index of this matrix' first tile in the tile buffer
+  int h, w;                   // matrix shape
+  int R, C;                   // tile grid (ceil(h/Th), ceil(w/Tw))
+  int unit_begin;             // first work unit of this entry
+  int ld;                     // element stride between gradient rows
+};
+void momentum_tile(const MomTileEntry* entries, int n_entries, int total_units, int Th, int Tw, void* tiles_bf16,
+                   float momentum, int nesterov, float grad_scale, int n_src, int grad_fp32, cudaStream_t stream);
+int momentum_tile_units(int R, int C, int Th);
+
+struct ApplyEntry {
+  void* param;
+  long long tile_base;
+  int h, w;
+  int R, C;
+  int unit_begin;
+  int group;        // row of the hyper-parameter table
+  float scale;      // lr multiplier (0.2*sqrt(max(block)) or 1)
+  int ld;
+};
+// p <- p*(1 - lr*wd) - lr*scale*U with U read from the tile buffer; lr = hyper[2g], wd = hyper[2g+1].
+void untile_apply(const ApplyEntry* entries, int n_entries, int total_units, int Th, int Tw, const void* tiles_bf16,
+                  const float* hyper, int param_fp32, cudaStream_t stream);
+
+// In-place per-tile Frobenius normalisation of a (B, m, n) bf16 buffer: X <- bf16(X / (||X||_F + eps)).
+void ns_normalize(void* tiles_bf16, long long n_tiles, long long tile_elems, float eps, cudaStream_t stream);
+
+struct AdamEntry {
+  void* param;
+  const void* grad;
+  void* m;
+  void* v;
+  long long numel;
+  long long unit_begin;
+  int group;
+  int pad;
+};
+// mode 0: HiMuon fallback (lerp moments, u = (m/bc1)/(sqrt(v)/sqrt(bc2)+eps), wd first)
+// mode 1: Muon fallback   (u = m/(eps+sqrt(v)), step = lr/(bc1/sqrt(bc2)), wd first)
+// mode 2: AdamW class     (u = m/(sqrt(v)+eps), step = lr*sqrt(bc2)/bc1, wd after the step)
+// `step` is a device scalar that the kernel's first thread increments after use (graph-replay safe);
+// hyper rows are (lr, wd, beta1, beta2, eps, unused...) with stride 8 floats per group.
+void adamw_multi(const AdamEntry* entries, int n_entries, long long total_units, const float* hyper, float* step,
+                 int mode, int param_fp32, int state_fp32, cudaStream_t stream);
+void adamw_step_advance(float* step, cudaStream_t stream);
+
+// ---------------------------------------------------------------- model kernels
+void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s);
+void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_accum,
+                 int rows, int cols, cudaStream_t s);
+// Per-head RMSNorm (optional) + rotary embedding on a (tokens, heads, 128) view with row stride `ld`.
+void headnorm_rope_fwd(const void* x, const void* w, void* y, float* rstd, const float* cos_sin, int tokens,
+                       int heads, int seq_len, long long ld_in, long long ld_out, float eps, int use_norm,
+                       cudaStream_t s);
+void headnorm_rope_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_accum,
+                       const float* cos_sin, int tokens, int heads, int seq_len, long long ld_dy, long long ld_x,
+                       long long ld_dx, int use_norm, cudaStream_t s);
+void swiglu_fwd(const void* gate, const void* up, void* out, long long rows, int cols, long long ld_g, long long ld_u,
+                long long ld_o, cudaStream_t s);
+void swiglu_bwd(const void* dout, const void* gate, const void* up, void* dgate, void* dup, long long rows, int cols,
+                long long ld_do, long long ld_g, long long ld_u, long long ld_dg, long long ld_du, cudaStream_t s);
+void embedding_fwd(const long long* ids, const void* table, void* out, long long tokens, int dim, cudaStream_t s);
+void embedding_bwd(const long long* ids, const void* dout, void* dtable, long long tokens, int dim, int table_fp32,
+                   cudaStream_t s);
+// Row-wise softmax cross-entropy on bf16 logits; overwrites logits with scale*(softmax - onehot).
+// Rows whose label is `ignore_index` get zero gradient.  loss_sum/count accumulate with atomics.
+void cross_entropy_fwd_bwd(void* logits, const long long* labels, float* loss_sum, float* count, float* lse_out,
+                           long long rows, int vocab, long long ld, float grad_scale, long long ignore_index,
+                           cudaStream_t s);
+void cast_copy(const void* src, void* dst, long long n, int src_fp32, int dst_fp32, float scale, cudaStream_t s);
+void bf16_add_to_f32(const void* src_bf16, float* dst, long long n, cudaStream_t s);
+
+// ---------------------------------------------------------------- attention (causal GQA, head_dim 128)
+// q: (B, S, Hq, 128), k/v: (B, S, Hkv, 128), o like q; all bf16 with token stride ld_* elements
+// (so q/k/v may be column slices of one fused projection output).  lse: (B, Hq, S) fp32.
+struct AttnArgs {
+  const void* q; const void* k; const void* v; void* o; float* lse;
+  const void* d_o; void* dq; void* dk; void* dv; float* delta;
+  int B, S, Hq, Hkv;
+  long long ld_q, ld_k, ld_v, ld_o, ld_do, ld_dq, ld_dk, ld_dv;
+  float scale;
+};
+void flash_attn_fwd(const AttnArgs& a, cudaStream_t s);
+void flash_attn_bwd(const AttnArgs& a, cudaStream_t s);
+
+// ---------------------------------------------------------------- fused tile-resident NS5
+// Five quintic Newton-Schulz iterations on (B, m, n) bf16 tiles with m <= n, m <= 128, n <= 128*... kept in
+// shared memory for the whole computation (see ns5_sm100.cu).
+bool ns5_fused_supported(int m, int n);
+void ns5_fused(const void* x_in, void* x_out, long long n_tiles, int m, int n, int steps, float eps, cudaStream_t s);
+
+}  // namespace himuon

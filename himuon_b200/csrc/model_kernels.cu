@@ -1,0 +1,535 @@
+// HBM-bound model kernels for the decoder (bf16 storage, fp32 math): RMSNorm, per-head
+// RMSNorm fused with rotary embedding, SwiGLU, embedding gather / scatter-add and the
+// softmax cross-entropy that turns a logits chunk into its gradient in place.
+// In the reference these are PyTorch / HF library calls
+// (transformers Qwen3/Llama modelling code reached from train.py:123-126).
+#include "himuon.h"
+#include "sm100_common.cuh"
+
+namespace himuon {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float block_sum_f(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+__device__ __forceinline__ float block_max_f(float v, float* red) {
+  v = warp_max(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : -INFINITY;
+  if (warp == 0) {
+    t = warp_max(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+// ------------------------------------------------------------------------------------------------ RMSNorm
+// One CTA per row; cols % 8 == 0.  y = bf16( bf16(x * rstd) * w )  (HF rounds to the input dtype before the weight).
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int cols, float eps) {
+  __shared__ float red[32];
+  const int nv = cols >> 3;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long long>(r) * cols);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      const uint4 v = xr[i];
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { const float a = bf16_lo(u[q]), b = bf16_hi(u[q]); ss += a * a + b * b; }
+    }
+    const float tot = block_sum_f(ss, red);
+    const float rs = rsqrtf(tot / cols + eps);
+    if (threadIdx.x == 0 && rstd) rstd[r] = rs;
+    uint4* yr = reinterpret_cast<uint4*>(y + static_cast<long long>(r) * cols);
+    const uint4* wr = reinterpret_cast<const uint4*>(w);
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      const uint4 v = xr[i];
+      const uint4 ww = wr[i];
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+      const uint32_t k[4] = {ww.x, ww.y, ww.z, ww.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        o[q] = pack_bf16x2(round_bf16(bf16_lo(u[q]) * rs) * bf16_lo(k[q]), round_bf16(bf16_hi(u[q]) * rs) * bf16_hi(k[q]));
+      yr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat));  dw += sum_rows dy * xhat  (fp32 atomics into dw_accum).
+// Each CTA owns a contiguous slab of rows and keeps its dw partial in registers (cols <= 8*256*kColIters).
+constexpr int kNormColIters = 8;
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_accum, int rows, int cols) {
+  __shared__ float red[32];
+  const int nv = cols >> 3;
+  float dwp[kNormColIters][8];
+#pragma unroll
+  for (int a = 0; a < kNormColIters; ++a)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) dwp[a][q] = 0.f;
+  const int rows_per = (rows + gridDim.x - 1) / gridDim.x;
+  const int r0 = blockIdx.x * rows_per;
+  const int r1 = min(rows, r0 + rows_per);
+  for (int r = r0; r < r1; ++r) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long long>(r) * cols);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + static_cast<long long>(r) * cols);
+    const uint4* wr = reinterpret_cast<const uint4*>(w);
+    const float rs = rstd[r];
+    float dot = 0.f;
+#pragma unroll
+    for (int a = 0; a < kNormColIters; ++a) {
+      const int i = threadIdx.x + a * 256;
+      if (i < nv) {
+        const uint4 xv = xr[i], gv = gr[i], wv = wr[i];
+        const uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w}, gu[4] = {gv.x, gv.y, gv.z, gv.w}, wu[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float xh0 = bf16_lo(xu[q]) * rs, xh1 = bf16_hi(xu[q]) * rs;
+          const float g0 = bf16_lo(gu[q]), g1 = bf16_hi(gu[q]);
+          dot += g0 * bf16_lo(wu[q]) * xh0 + g1 * bf16_hi(wu[q]) * xh1;
+          dwp[a][2 * q] += g0 * xh0;
+          dwp[a][2 * q + 1] += g1 * xh1;
+        }
+      }
+    }
+    const float mean = block_sum_f(dot, red) / cols;
+    uint4* dr = reinterpret_cast<uint4*>(dx + static_cast<long long>(r) * cols);
+#pragma unroll
+    for (int a = 0; a < kNormColIters; ++a) {
+      const int i = threadIdx.x + a * 256;
+      if (i < nv) {
+        const uint4 xv = xr[i], gv = gr[i], wv = wr[i];
+        const uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w}, gu[4] = {gv.x, gv.y, gv.z, gv.w}, wu[4] = {wv.x, wv.y, wv.z, wv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float xh0 = bf16_lo(xu[q]) * rs, xh1 = bf16_hi(xu[q]) * rs;
+          o[q] = pack_bf16x2(rs * (bf16_lo(gu[q]) * bf16_lo(wu[q]) - xh0 * mean),
+                             rs * (bf16_hi(gu[q]) * bf16_hi(wu[q]) - xh1 * mean));
+        }
+        dr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+  if (dw_accum) {
+#pragma unroll
+    for (int a = 0; a < kNormColIters; ++a) {
+      const int i = threadIdx.x + a * 256;
+      if (i < nv) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) atomicAdd(dw_accum + i * 8 + q, dwp[a][q]);
+      }
+    }
+  }
+}
+
+void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s) {
+  if (rows <= 0) return;
+  if (cols % 8) throw std::runtime_error("himuon rmsnorm: hidden size must be a multiple of 8");
+  const int grid = rows < num_sms() * 8 ? rows : num_sms() * 8;
+  rmsnorm_fwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
+                                          reinterpret_cast<__nv_bfloat16*>(y), rstd, rows, cols, eps);
+}
+void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_accum, int rows,
+                 int cols, cudaStream_t s) {
+  if (rows <= 0) return;
+  if (cols % 8 || cols > 8 * 256 * kNormColIters) throw std::runtime_error("himuon rmsnorm_bwd: unsupported hidden size");
+  const int grid = rows < num_sms() * 4 ? rows : num_sms() * 4;
+  rmsnorm_bwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
+                                          reinterpret_cast<const __nv_bfloat16*>(w), rstd, reinterpret_cast<__nv_bfloat16*>(dx),
+                                          dw_accum, rows, cols);
+}
+
+// ------------------------------------------------------------------------------------------------ head-norm + RoPE
+// One warp per (token, head) vector of 128 elements: lane l holds elements {2l, 2l+1} of the first
+// half (i.e. 4 values: first-half pair and the matching second-half pair).
+// cos_sin: (seq_len, 64, 2) fp32.  Rotate-half convention:
+//   y[i]      = xn[i]*cos[i] - xn[i+64]*sin[i]
+//   y[i+64]   = xn[i+64]*cos[i] + xn[i]*sin[i]
+__global__ void __launch_bounds__(256)
+headnorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                         __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, const float* __restrict__ cos_sin,
+                         long long n_vec, int heads, int seq_len, long long ld_in, long long ld_out, float eps,
+                         int use_norm) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  float w0 = 1.f, w1 = 1.f, w2 = 1.f, w3 = 1.f;
+  if (use_norm) {
+    const uint32_t a = reinterpret_cast<const uint32_t*>(w)[lane], b = reinterpret_cast<const uint32_t*>(w)[32 + lane];
+    w0 = bf16_lo(a); w1 = bf16_hi(a); w2 = bf16_lo(b); w3 = bf16_hi(b);
+  }
+  for (long long vi = warp0; vi < n_vec; vi += nwarps) {
+    const long long tok = vi / heads;
+    const int head = static_cast<int>(vi - tok * heads);
+    const int pos = static_cast<int>(tok % seq_len);
+    const __nv_bfloat16* xp = x + tok * ld_in + head * 128;
+    const uint32_t a = reinterpret_cast<const uint32_t*>(xp)[lane], b = reinterpret_cast<const uint32_t*>(xp)[32 + lane];
+    float x0 = bf16_lo(a), x1 = bf16_hi(a), x2 = bf16_lo(b), x3 = bf16_hi(b);
+    if (use_norm) {
+      const float ss = warp_sum(x0 * x0 + x1 * x1 + x2 * x2 + x3 * x3);
+      const float rs = rsqrtf(ss * (1.f / 128.f) + eps);
+      if (lane == 0 && rstd) rstd[vi] = rs;
+      x0 = round_bf16(round_bf16(x0 * rs) * w0); x1 = round_bf16(round_bf16(x1 * rs) * w1);
+      x2 = round_bf16(round_bf16(x2 * rs) * w2); x3 = round_bf16(round_bf16(x3 * rs) * w3);
+    }
+    const float4 cs = reinterpret_cast<const float4*>(cos_sin + static_cast<long long>(pos) * 128)[lane];  // c0,s0,c1,s1
+    const float y0 = x0 * cs.x - x2 * cs.y, y2 = x2 * cs.x + x0 * cs.y;
+    const float y1 = x1 * cs.z - x3 * cs.w, y3 = x3 * cs.z + x1 * cs.w;
+    __nv_bfloat16* yp = y + tok * ld_out + head * 128;
+    reinterpret_cast<uint32_t*>(yp)[lane] = pack_bf16x2(y0, y1);
+    reinterpret_cast<uint32_t*>(yp)[32 + lane] = pack_bf16x2(y2, y3);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+headnorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                         const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                         __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_accum,
+                         const float* __restrict__ cos_sin, long long n_vec, int heads, int seq_len, long long ld_dy,
+                         long long ld_x, long long ld_dx, int use_norm) {
+  __shared__ float sdw[128];
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x < 128) sdw[threadIdx.x] = 0.f;
+  __syncthreads();
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  float w0 = 1.f, w1 = 1.f, w2 = 1.f, w3 = 1.f;
+  if (use_norm) {
+    const uint32_t a = reinterpret_cast<const uint32_t*>(w)[lane], b = reinterpret_cast<const uint32_t*>(w)[32 + lane];
+    w0 = bf16_lo(a); w1 = bf16_hi(a); w2 = bf16_lo(b); w3 = bf16_hi(b);
+  }
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  for (long long vi = warp0; vi < n_vec; vi += nwarps) {
+    const long long tok = vi / heads;
+    const int head = static_cast<int>(vi - tok * heads);
+    const int pos = static_cast<int>(tok % seq_len);
+    const __nv_bfloat16* gp = dy + tok * ld_dy + head * 128;
+    const uint32_t ga = reinterpret_cast<const uint32_t*>(gp)[lane], gb = reinterpret_cast<const uint32_t*>(gp)[32 + lane];
+    const float g0 = bf16_lo(ga), g1 = bf16_hi(ga), g2 = bf16_lo(gb), g3 = bf16_hi(gb);
+    const float4 cs = reinterpret_cast<const float4*>(cos_sin + static_cast<long long>(pos) * 128)[lane];
+    // transpose of the rotation
+    float d0 = g0 * cs.x + g2 * cs.y, d2 = g2 * cs.x - g0 * cs.y;
+    float d1 = g1 * cs.z + g3 * cs.w, d3 = g3 * cs.z - g1 * cs.w;
+    if (use_norm) {
+      const __nv_bfloat16* xp = x + tok * ld_x + head * 128;
+      const uint32_t xa = reinterpret_cast<const uint32_t*>(xp)[lane], xb = reinterpret_cast<const uint32_t*>(xp)[32 + lane];
+      const float rs = rstd[vi];
+      const float h0 = bf16_lo(xa) * rs, h1 = bf16_hi(xa) * rs, h2 = bf16_lo(xb) * rs, h3 = bf16_hi(xb) * rs;
+      a0 += d0 * h0; a1 += d1 * h1; a2 += d2 * h2; a3 += d3 * h3;
+      const float mean = warp_sum(d0 * w0 * h0 + d1 * w1 * h1 + d2 * w2 * h2 + d3 * w3 * h3) * (1.f / 128.f);
+      d0 = rs * (d0 * w0 - h0 * mean); d1 = rs * (d1 * w1 - h1 * mean);
+      d2 = rs * (d2 * w2 - h2 * mean); d3 = rs * (d3 * w3 - h3 * mean);
+    }
+    __nv_bfloat16* op = dx + tok * ld_dx + head * 128;
+    reinterpret_cast<uint32_t*>(op)[lane] = pack_bf16x2(d0, d1);
+    reinterpret_cast<uint32_t*>(op)[32 + lane] = pack_bf16x2(d2, d3);
+  }
+  if (use_norm && dw_accum) {
+    atomicAdd(&sdw[2 * lane], a0); atomicAdd(&sdw[2 * lane + 1], a1);
+    atomicAdd(&sdw[64 + 2 * lane], a2); atomicAdd(&sdw[64 + 2 * lane + 1], a3);
+    __syncthreads();
+    if (threadIdx.x < 128) atomicAdd(dw_accum + threadIdx.x, sdw[threadIdx.x]);
+  }
+}
+
+void headnorm_rope_fwd(const void* x, const void* w, void* y, float* rstd, const float* cos_sin, int tokens, int heads,
+                       int seq_len, long long ld_in, long long ld_out, float eps, int use_norm, cudaStream_t s) {
+  const long long n_vec = static_cast<long long>(tokens) * heads;
+  if (n_vec <= 0) return;
+  const long long blocks = (n_vec + 7) / 8;
+  const int grid = static_cast<int>(blocks < num_sms() * 8 ? blocks : num_sms() * 8);
+  headnorm_rope_fwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
+                                                reinterpret_cast<__nv_bfloat16*>(y), rstd, cos_sin, n_vec, heads, seq_len,
+                                                ld_in, ld_out, eps, use_norm);
+}
+void headnorm_rope_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_accum,
+                       const float* cos_sin, int tokens, int heads, int seq_len, long long ld_dy, long long ld_x,
+                       long long ld_dx, int use_norm, cudaStream_t s) {
+  const long long n_vec = static_cast<long long>(tokens) * heads;
+  if (n_vec <= 0) return;
+  const long long blocks = (n_vec + 7) / 8;
+  const int grid = static_cast<int>(blocks < num_sms() * 4 ? blocks : num_sms() * 4);
+  headnorm_rope_bwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
+                                                reinterpret_cast<const __nv_bfloat16*>(w), rstd, reinterpret_cast<__nv_bfloat16*>(dx),
+                                                dw_accum, cos_sin, n_vec, heads, seq_len, ld_dy, ld_x, ld_dx, use_norm);
+}
+
+// ------------------------------------------------------------------------------------------------ SwiGLU
+__global__ void __launch_bounds__(256)
+swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+                  __nv_bfloat16* __restrict__ out, long long rows, int cols, long long ld_g, long long ld_u, long long ld_o) {
+  const int vpr = cols >> 3;
+  const long long total = rows * vpr;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vpr;
+    const int c = static_cast<int>(i - r * vpr) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gate + r * ld_g + c);
+    const uint4 u = *reinterpret_cast<const uint4*>(up + r * ld_u + c);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float g0 = bf16_lo(gw[q]), g1 = bf16_hi(gw[q]);
+      const float s0 = round_bf16(g0 / (1.f + __expf(-g0))), s1 = round_bf16(g1 / (1.f + __expf(-g1)));
+      o[q] = pack_bf16x2(s0 * bf16_lo(uw[q]), s1 * bf16_hi(uw[q]));
+    }
+    *reinterpret_cast<uint4*>(out + r * ld_o + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ gate,
+                  const __nv_bfloat16* __restrict__ up, __nv_bfloat16* __restrict__ dgate, __nv_bfloat16* __restrict__ dup,
+                  long long rows, int cols, long long ld_do, long long ld_g, long long ld_u, long long ld_dg, long long ld_du) {
+  const int vpr = cols >> 3;
+  const long long total = rows * vpr;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vpr;
+    const int c = static_cast<int>(i - r * vpr) * 8;
+    const uint4 d = *reinterpret_cast<const uint4*>(dout + r * ld_do + c);
+    const uint4 g = *reinterpret_cast<const uint4*>(gate + r * ld_g + c);
+    const uint4 u = *reinterpret_cast<const uint4*>(up + r * ld_u + c);
+    const uint32_t dw[4] = {d.x, d.y, d.z, d.w}, gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t og[4], ou[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float gg[2] = {bf16_lo(gw[q]), bf16_hi(gw[q])}, uu[2] = {bf16_lo(uw[q]), bf16_hi(uw[q])}, dd[2] = {bf16_lo(dw[q]), bf16_hi(dw[q])};
+      float rg[2], ru[2];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const float sig = 1.f / (1.f + __expf(-gg[t]));
+        const float silu = gg[t] * sig;
+        ru[t] = dd[t] * silu;
+        rg[t] = dd[t] * uu[t] * (sig * (1.f + gg[t] * (1.f - sig)));
+      }
+      og[q] = pack_bf16x2(rg[0], rg[1]);
+      ou[q] = pack_bf16x2(ru[0], ru[1]);
+    }
+    *reinterpret_cast<uint4*>(dgate + r * ld_dg + c) = make_uint4(og[0], og[1], og[2], og[3]);
+    *reinterpret_cast<uint4*>(dup + r * ld_du + c) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+  }
+}
+static int ew_grid(long long work_items) {
+  const long long blocks = (work_items + 255) / 256;
+  const long long cap = static_cast<long long>(num_sms()) * 16;
+  return static_cast<int>(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
+}
+void swiglu_fwd(const void* gate, const void* up, void* out, long long rows, int cols, long long ld_g, long long ld_u,
+                long long ld_o, cudaStream_t s) {
+  if (rows <= 0) return;
+  if (cols % 8 || ld_g % 8 || ld_u % 8 || ld_o % 8) throw std::runtime_error("himuon swiglu: sizes must be multiples of 8");
+  swiglu_fwd_kernel<<<ew_grid(rows * (cols / 8)), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(gate),
+      reinterpret_cast<const __nv_bfloat16*>(up), reinterpret_cast<__nv_bfloat16*>(out), rows, cols, ld_g, ld_u, ld_o);
+}
+void swiglu_bwd(const void* dout, const void* gate, const void* up, void* dgate, void* dup, long long rows, int cols,
+                long long ld_do, long long ld_g, long long ld_u, long long ld_dg, long long ld_du, cudaStream_t s) {
+  if (rows <= 0) return;
+  if (cols % 8 || ld_do % 8 || ld_g % 8 || ld_u % 8 || ld_dg % 8 || ld_du % 8)
+    throw std::runtime_error("himuon swiglu: sizes must be multiples of 8");
+  swiglu_bwd_kernel<<<ew_grid(rows * (cols / 8)), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(dout),
+      reinterpret_cast<const __nv_bfloat16*>(gate), reinterpret_cast<const __nv_bfloat16*>(up),
+      reinterpret_cast<__nv_bfloat16*>(dgate), reinterpret_cast<__nv_bfloat16*>(dup), rows, cols, ld_do, ld_g, ld_u, ld_dg, ld_du);
+}
+
+// ------------------------------------------------------------------------------------------------ embedding
+__global__ void __launch_bounds__(256)
+embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                     __nv_bfloat16* __restrict__ out, long long tokens, int dim) {
+  const int vpr = dim >> 3;
+  const long long total = tokens * vpr;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / vpr;
+    const int c = static_cast<int>(i - t * vpr);
+    reinterpret_cast<uint4*>(out + t * dim)[c] = reinterpret_cast<const uint4*>(table + ids[t] * dim)[c];
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(256)
+embedding_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dout, T* __restrict__ dtable,
+                     long long tokens, int dim) {
+  const int ppr = dim >> 1;
+  const long long total = tokens * ppr;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / ppr;
+    const int c = static_cast<int>(i - t * ppr) * 2;
+    const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(dout + t * dim + c);
+    if constexpr (sizeof(T) == 2) {
+      atomicAdd(reinterpret_cast<__nv_bfloat162*>(dtable + ids[t] * dim + c), g);
+    } else {
+      atomicAdd(reinterpret_cast<float*>(dtable) + ids[t] * dim + c, __low2float(g));
+      atomicAdd(reinterpret_cast<float*>(dtable) + ids[t] * dim + c + 1, __high2float(g));
+    }
+  }
+}
+void embedding_fwd(const long long* ids, const void* table, void* out, long long tokens, int dim, cudaStream_t s) {
+  if (tokens <= 0) return;
+  if (dim % 8) throw std::runtime_error("himuon embedding: dim must be a multiple of 8");
+  embedding_fwd_kernel<<<ew_grid(tokens * (dim / 8)), 256, 0, s>>>(ids, reinterpret_cast<const __nv_bfloat16*>(table),
+                                                                  reinterpret_cast<__nv_bfloat16*>(out), tokens, dim);
+}
+void embedding_bwd(const long long* ids, const void* dout, void* dtable, long long tokens, int dim, int table_fp32,
+                   cudaStream_t s) {
+  if (tokens <= 0) return;
+  if (table_fp32)
+    embedding_bwd_kernel<float><<<ew_grid(tokens * (dim / 2)), 256, 0, s>>>(ids, reinterpret_cast<const __nv_bfloat16*>(dout),
+                                                                           reinterpret_cast<float*>(dtable), tokens, dim);
+  else
+    embedding_bwd_kernel<__nv_bfloat16><<<ew_grid(tokens * (dim / 2)), 256, 0, s>>>(ids, reinterpret_cast<const __nv_bfloat16*>(dout),
+                                                                                   reinterpret_cast<__nv_bfloat16*>(dtable), tokens, dim);
+}
+
+// ------------------------------------------------------------------------------------------------ cross entropy
+// One CTA per row of a (rows, vocab) bf16 logits chunk: online max / sum-exp in pass 1, then the row is
+// rewritten as grad_scale * (softmax - onehot) in pass 2 (the re-read is served from L2).
+__global__ void __launch_bounds__(1024)
+cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
+                     float* __restrict__ loss_sum, float* __restrict__ count, float* __restrict__ lse_out,
+                     long long rows, int vocab, long long ld, float grad_scale, long long ignore_index) {
+  __shared__ float red[32];
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    __nv_bfloat16* row = logits + r * ld;
+    const long long label = labels[r];
+    const bool valid = label != ignore_index;   // uniform over the block
+    const bool vec = ((vocab & 7) == 0) && ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
+    if (!valid) {
+      if (vec) {
+        for (int i = threadIdx.x; i < (vocab >> 3); i += blockDim.x) reinterpret_cast<uint4*>(row)[i] = make_uint4(0, 0, 0, 0);
+      } else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) row[i] = __float2bfloat16_rn(0.f);
+      }
+      if (threadIdx.x == 0 && lse_out) lse_out[r] = 0.f;
+      continue;
+    }
+    float mx = -INFINITY, sum = 0.f;
+    if (vec) {
+      for (int i = threadIdx.x; i < (vocab >> 3); i += blockDim.x) {
+        const uint4 v = reinterpret_cast<const uint4*>(row)[i];
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+        float f[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { f[2 * q] = bf16_lo(u[q]); f[2 * q + 1] = bf16_hi(u[q]); }
+        float lm = f[0];
+#pragma unroll
+        for (int q = 1; q < 8; ++q) lm = fmaxf(lm, f[q]);
+        if (lm > mx) { sum *= __expf(mx - lm); mx = lm; }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) sum += __expf(f[q] - mx);
+      }
+    } else {
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float f = __bfloat162float(row[i]);
+        if (f > mx) { sum *= __expf(mx - f); mx = f; }
+        sum += __expf(f - mx);
+      }
+    }
+    const float gmx = block_max_f(mx, red);
+    sum = (mx == -INFINITY) ? 0.f : sum * __expf(mx - gmx);
+    const float gsum = block_sum_f(sum, red);
+    const float lse = gmx + logf(gsum);
+    if (threadIdx.x == 0) {
+      const float tgt = __bfloat162float(row[label]);
+      atomicAdd(loss_sum, lse - tgt);
+      atomicAdd(count, 1.f);
+      if (lse_out) lse_out[r] = lse;
+    }
+    __syncthreads();  // the target logit is read before anyone overwrites it
+    if (vec) {
+      for (int i = threadIdx.x; i < (vocab >> 3); i += blockDim.x) {
+        const uint4 v = reinterpret_cast<const uint4*>(row)[i];
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float p0 = __expf(bf16_lo(u[q]) - lse), p1 = __expf(bf16_hi(u[q]) - lse);
+          const long long c = static_cast<long long>(i) * 8 + 2 * q;
+          if (c == label) p0 -= 1.f;
+          if (c + 1 == label) p1 -= 1.f;
+          o[q] = pack_bf16x2(p0 * grad_scale, p1 * grad_scale);
+        }
+        reinterpret_cast<uint4*>(row)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    } else {
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        float p = __expf(__bfloat162float(row[i]) - lse);
+        if (i == label) p -= 1.f;
+        row[i] = __float2bfloat16_rn(p * grad_scale);
+      }
+    }
+    __syncthreads();
+  }
+}
+void cross_entropy_fwd_bwd(void* logits, const long long* labels, float* loss_sum, float* count, float* lse_out,
+                           long long rows, int vocab, long long ld, float grad_scale, long long ignore_index,
+                           cudaStream_t s) {
+  if (rows <= 0) return;
+  const long long cap = static_cast<long long>(num_sms()) * 2;
+  const int grid = static_cast<int>(rows < cap ? rows : cap);
+  cross_entropy_kernel<<<grid, 1024, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(logits), labels, loss_sum, count, lse_out, rows,
+                                             vocab, ld, grad_scale, ignore_index);
+}
+
+// ------------------------------------------------------------------------------------------------ casts
+template <typename S, typename D>
+__global__ void cast_copy_kernel(const S* __restrict__ src, D* __restrict__ dst, long long n, float scale) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float v;
+    if constexpr (sizeof(S) == 2) v = __bfloat162float(src[i]); else v = src[i];
+    v *= scale;
+    if constexpr (sizeof(D) == 2) dst[i] = __float2bfloat16_rn(v); else dst[i] = v;
+  }
+}
+void cast_copy(const void* src, void* dst, long long n, int src_fp32, int dst_fp32, float scale, cudaStream_t s) {
+  if (n <= 0) return;
+  const int grid = ew_grid(n);
+  if (src_fp32 && dst_fp32) cast_copy_kernel<float, float><<<grid, 256, 0, s>>>((const float*)src, (float*)dst, n, scale);
+  else if (src_fp32) cast_copy_kernel<float, __nv_bfloat16><<<grid, 256, 0, s>>>((const float*)src, (__nv_bfloat16*)dst, n, scale);
+  else if (dst_fp32) cast_copy_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>((const __nv_bfloat16*)src, (float*)dst, n, scale);
+  else cast_copy_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, n, scale);
+}
+__global__ void bf16_add_to_f32_kernel(const __nv_bfloat16* __restrict__ src, float* __restrict__ dst, long long n) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] += __bfloat162float(src[i]);
+}
+void bf16_add_to_f32(const void* src, float* dst, long long n, cudaStream_t s) {
+  if (n <= 0) return;
+  bf16_add_to_f32_kernel<<<ew_grid(n), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(src), dst, n);
+}
+
+}  // namespace himuon
