@@ -168,14 +168,17 @@ static void embedding_bwd(const at::Tensor& ids, const at::Tensor& dout, at::Ten
   himuon::embedding_bwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), dout.data_ptr(), dtable.data_ptr(), ids.numel(), (int)dtable.size(1), is_f32(dtable) ? 1 : 0, cur_stream());
 }
 static void cross_entropy(at::Tensor& logits, const at::Tensor& labels, at::Tensor& loss_sum, at::Tensor& count,
-                          const c10::optional<at::Tensor>& lse, double grad_scale, int64_t ignore_index) {
+                          const c10::optional<at::Tensor>& lse, double grad_scale,
+                          const c10::optional<at::Tensor>& scale_dev, int64_t ignore_index) {
   HM_CHECK(logits.is_cuda() && is_bf16(logits) && logits.dim() == 2 && logits.stride(1) == 1, "cross_entropy: logits must be 2-D bf16");
   HM_CHECK(labels.scalar_type() == at::kLong && labels.is_contiguous() && labels.numel() == logits.size(0), "cross_entropy: labels");
   HM_CHECK(is_f32(loss_sum) && is_f32(count), "cross_entropy: accumulators must be fp32");
+  if (scale_dev.has_value()) HM_CHECK(scale_dev->is_cuda() && is_f32(*scale_dev) && scale_dev->numel() == 1, "cross_entropy: scale_dev must be one fp32 on the device");
   const c10::cuda::CUDAGuard guard(logits.device());
   himuon::cross_entropy_fwd_bwd(logits.data_ptr(), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()), loss_sum.data_ptr<float>(),
                                 count.data_ptr<float>(), lse.has_value() ? lse->data_ptr<float>() : nullptr, logits.size(0),
-                                (int)logits.size(1), logits.stride(0), (float)grad_scale, ignore_index, cur_stream());
+                                (int)logits.size(1), logits.stride(0), (float)grad_scale,
+                                scale_dev.has_value() ? scale_dev->data_ptr<float>() : nullptr, ignore_index, cur_stream());
 }
 
 static void flash_attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, at::Tensor& o, at::Tensor& lse,

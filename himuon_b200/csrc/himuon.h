@@ -64,7 +64,8 @@ struct ApplyEntry {
   float scale;      // lr multiplier (0.2*sqrt(max(block)) or 1)
   int ld;
 };
-// p <- p*(1 - lr*wd) - lr*scale*U with U read from the tile buffer; lr = hyper[2g], wd = hyper[2g+1].
+// p <- p*(1 - lr*wd) - lr*scale*U with U read from the tile buffer; lr = hyper[8g], wd = hyper[8g+1]
+// (the same 8-float rows as adamw_multi).
 void untile_apply(const ApplyEntry* entries, int n_entries, int total_units, int Th, int Tw, const void* tiles_bf16,
                   const float* hyper, int param_fp32, cudaStream_t stream);
 
@@ -110,9 +111,10 @@ void embedding_bwd(const long long* ids, const void* dout, void* dtable, long lo
                    cudaStream_t s);
 // Row-wise softmax cross-entropy on bf16 logits; overwrites logits with scale*(softmax - onehot).
 // Rows whose label is `ignore_index` get zero gradient.  loss_sum/count accumulate with atomics.
+// The gradient scale is grad_scale * (*scale_dev) when scale_dev is given (a device scalar such as 1/n_valid).
 void cross_entropy_fwd_bwd(void* logits, const long long* labels, float* loss_sum, float* count, float* lse_out,
-                           long long rows, int vocab, long long ld, float grad_scale, long long ignore_index,
-                           cudaStream_t s);
+                           long long rows, int vocab, long long ld, float grad_scale, const float* scale_dev,
+                           long long ignore_index, cudaStream_t s);
 void cast_copy(const void* src, void* dst, long long n, int src_fp32, int dst_fp32, float scale, cudaStream_t s);
 void bf16_add_to_f32(const void* src_bf16, float* dst, long long n, cudaStream_t s);
 

@@ -419,8 +419,10 @@ void embedding_bwd(const long long* ids, const void* dout, void* dtable, long lo
 __global__ void __launch_bounds__(1024)
 cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
                      float* __restrict__ loss_sum, float* __restrict__ count, float* __restrict__ lse_out,
-                     long long rows, int vocab, long long ld, float grad_scale, long long ignore_index) {
+                     long long rows, int vocab, long long ld, float grad_scale, const float* __restrict__ scale_dev,
+                     long long ignore_index) {
   __shared__ float red[32];
+  if (scale_dev) grad_scale *= *scale_dev;
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
     __nv_bfloat16* row = logits + r * ld;
     const long long label = labels[r];
@@ -494,13 +496,13 @@ cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __rest
   }
 }
 void cross_entropy_fwd_bwd(void* logits, const long long* labels, float* loss_sum, float* count, float* lse_out,
-                           long long rows, int vocab, long long ld, float grad_scale, long long ignore_index,
-                           cudaStream_t s) {
+                           long long rows, int vocab, long long ld, float grad_scale, const float* scale_dev,
+                           long long ignore_index, cudaStream_t s) {
   if (rows <= 0) return;
   const long long cap = static_cast<long long>(num_sms()) * 2;
   const int grid = static_cast<int>(rows < cap ? rows : cap);
   cross_entropy_kernel<<<grid, 1024, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(logits), labels, loss_sum, count, lse_out, rows,
-                                             vocab, ld, grad_scale, ignore_index);
+                                             vocab, ld, grad_scale, scale_dev, ignore_index);
 }
 
 // ------------------------------------------------------------------------------------------------ casts

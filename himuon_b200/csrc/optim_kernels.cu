@@ -146,7 +146,7 @@ untile_apply_kernel(const ApplyEntry* __restrict__ entries, int n_entries, int t
   for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
     const int ei = find_entry(entries, n_entries, unit);
     const ApplyEntry e = entries[ei];
-    const float lr = hyper[2 * e.group], wd = hyper[2 * e.group + 1];
+    const float lr = hyper[8 * e.group], wd = hyper[8 * e.group + 1];
     const float decay = wd > 0.f ? 1.f - lr * wd : 1.f;
     const float step = lr * e.scale;
     const int local = unit - e.unit_begin;

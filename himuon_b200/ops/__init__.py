@@ -1,0 +1,406 @@
+"""Differentiable ops of the decoder and the optimizers.
+
+On a CUDA device with bf16 tensors every op launches the hand-written sm_100a kernels of
+``himuon_b200/csrc`` (and raises if the extension is missing); anywhere else (CPU, fp32) the
+pure-PyTorch implementations of :mod:`himuon_b200.ops.reference` run and autograd
+differentiates them.  A launch counter records how many of the library's own kernels were
+issued (``launch_count()``), which the benchmark reports.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import reference as ref
+from .. import _ext
+
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    return _LAUNCHES
+
+
+def _count(n: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
+def use_kernels(t: torch.Tensor) -> bool:
+    """True when ``t`` runs on the sm_100a kernel path (CUDA + bf16)."""
+    return t.is_cuda and t.dtype == torch.bfloat16
+
+
+def check_status() -> None:
+    """Raise if any kernel's bounded wait ran out since the last check (synchronises)."""
+    code = _ext.ext().status(True)
+    if code:
+        raise RuntimeError(f"himuon_b200: a device-side wait timed out (status code {code}); results are invalid")
+
+
+# ------------------------------------------------------------------------------------------- GEMM
+def gemm(a, b, *, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, aux=None, out=None,
+         out_dtype=None, round_acc=False, max_ctas=0):
+    """``alpha * op(a) @ op(b) + beta * aux`` for 2-D or batched 3-D operands (no autograd)."""
+    if use_kernels(a):
+        M = a.shape[-1] if trans_a else a.shape[-2]
+        N = b.shape[-2] if trans_b else b.shape[-1]
+        if out is None:
+            out = torch.empty(*a.shape[:-2], M, N, device=a.device, dtype=out_dtype or torch.bfloat16)
+        if a.stride(-1) != 1:
+            a = a.contiguous()
+        if b.stride(-1) != 1:
+            b = b.contiguous()
+        _ext.ext().gemm(a, b, out, aux, trans_a, trans_b, float(alpha), float(beta), bool(round_acc), int(max_ctas))
+        _count()
+        return out
+    A = a.transpose(-2, -1) if trans_a else a
+    B = b.transpose(-2, -1) if trans_b else b
+    if a.dtype == torch.bfloat16:
+        res = alpha * (A.float() @ B.float())
+        if round_acc:
+            res = res.bfloat16().float()
+    else:
+        res = alpha * (A @ B)
+    if aux is not None and beta != 0.0:
+        res = res + beta * aux.to(res.dtype)
+    res = res.to(out_dtype or a.dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+class GradSink:
+    """Destination of a weight gradient that bypasses autograd accumulation.
+
+    ``buffer`` is a persistent ``(H, W)`` view (for example one slot of a bank's gradient
+    buffer).  The first write after ``reset()`` overwrites, later writes accumulate.
+    """
+
+    __slots__ = ("buffer", "fresh")
+
+    def __init__(self, buffer: torch.Tensor):
+        self.buffer = buffer
+        self.fresh = True
+
+    def reset(self):
+        self.fresh = True
+
+    def add_wgrad(self, dy2d: torch.Tensor, x2d: torch.Tensor) -> None:
+        gemm(dy2d, x2d, trans_a=True, out=self.buffer, aux=None if self.fresh else self.buffer,
+             beta=0.0 if self.fresh else 1.0)
+        self.fresh = False
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, sink, param):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w, trans_b=True)
+        ctx.save_for_backward(x2, w)
+        ctx.sink = sink
+        ctx.param = param
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = gemm(dy2, w).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.sink is not None:
+            ctx.sink.add_wgrad(dy2, x2)
+        elif ctx.needs_input_grad[1]:
+            p = ctx.param
+            if p is not None and p.grad is not None and p.grad.dtype in (torch.bfloat16, torch.float32) \
+                    and p.grad.is_contiguous():
+                # accumulate straight into the existing gradient (no temporary, no extra add kernel)
+                gemm(dy2, x2, trans_a=True, out=p.grad, aux=p.grad, beta=1.0)
+            else:
+                dw = gemm(dy2, x2, trans_a=True)
+        return dx, dw, None, None
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, sink: GradSink | None = None) -> torch.Tensor:
+    """``x @ w.T``.  With ``sink`` the weight gradient is written there instead of returned."""
+    if use_kernels(x) and w.dtype == torch.bfloat16:
+        param = w if isinstance(w, torch.nn.Parameter) else None
+        return _LinearFn.apply(x, w, sink, param)
+    if sink is not None:
+        return _SinkLinearRef.apply(x, w, sink)
+    return torch.nn.functional.linear(x, w)
+
+
+class _SinkLinearRef(torch.autograd.Function):
+    """CPU / fp32 counterpart of the sink path (used by the bank engine off-GPU)."""
+
+    @staticmethod
+    def forward(ctx, x, w, sink):
+        ctx.save_for_backward(x, w)
+        ctx.sink = sink
+        return torch.nn.functional.linear(x, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        dw = (dy2.float().t() @ x2.float()).to(ctx.sink.buffer.dtype)
+        if ctx.sink.fresh:
+            ctx.sink.buffer.copy_(dw)
+            ctx.sink.fresh = False
+        else:
+            ctx.sink.buffer.add_(dw)
+        return (dy2 @ w).view(x.shape), None, None
+
+
+# ------------------------------------------------------------------------------------------- norms / rope
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        y = torch.empty_like(x2)
+        rstd = torch.empty(x2.shape[0], device=x.device, dtype=torch.float32)
+        _ext.ext().rmsnorm_fwd(x2, w, y, rstd, float(eps))
+        _count()
+        ctx.save_for_backward(x2, w, rstd)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dx = torch.empty_like(x2)
+        dw = torch.zeros(w.numel(), device=w.device, dtype=torch.float32)
+        _ext.ext().rmsnorm_bwd(dy2, x2, w, rstd, dx, dw)
+        _count(2)
+        return dx.view(dy.shape), dw.to(w.dtype), None
+
+
+def rmsnorm(x, w, eps: float):
+    if use_kernels(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384:
+        return _RMSNormFn.apply(x, w, eps)
+    return ref.rmsnorm(x, w, eps)
+
+
+class _HeadNormRopeFn(torch.autograd.Function):
+    """Per-head RMSNorm (optional) + RoPE on a ``(tokens, heads*128)`` view."""
+
+    @staticmethod
+    def forward(ctx, x, w, cos_sin, heads, seq_len, eps):
+        y = torch.empty(x.shape[0], heads * 128, device=x.device, dtype=x.dtype)
+        rstd = torch.empty(x.shape[0] * heads, device=x.device, dtype=torch.float32) if w is not None else None
+        _ext.ext().headnorm_rope_fwd(x, w, y, rstd, cos_sin, heads, seq_len, float(eps))
+        _count()
+        ctx.save_for_backward(x, w, rstd, cos_sin)
+        ctx.heads, ctx.seq_len = heads, seq_len
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd, cos_sin = ctx.saved_tensors
+        if dy.stride(-1) != 1:
+            dy = dy.contiguous()
+        dx = torch.empty(dy.shape[0], ctx.heads * 128, device=dy.device, dtype=dy.dtype)
+        dw = torch.zeros(128, device=dy.device, dtype=torch.float32) if w is not None else None
+        _ext.ext().headnorm_rope_bwd(dy, x if w is not None else None, w, rstd, dx, dw, cos_sin, ctx.heads, ctx.seq_len)
+        _count(2 if w is not None else 1)
+        return dx, (dw.to(w.dtype) if w is not None else None), None, None, None, None
+
+
+def head_norm_rope(x2d, w, cos_sin, heads: int, seq_len: int, head_dim: int, eps: float):
+    """``x2d``: ``(B*S, heads*head_dim)`` (may be a column slice).  Returns the same layout."""
+    if use_kernels(x2d) and head_dim == 128:
+        return _HeadNormRopeFn.apply(x2d, w, cos_sin, heads, seq_len, eps)
+    T = x2d.shape[0]
+    x = x2d.reshape(T // seq_len, seq_len, heads, head_dim)
+    if w is not None:
+        x = ref.rmsnorm(x, w, eps)
+    return ref.apply_rope(x, cos_sin).reshape(T, heads * head_dim)
+
+
+# ------------------------------------------------------------------------------------------- attention
+class _FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, B, S, Hq, Hkv, scale):
+        o = torch.empty(q.shape[0], Hq * 128, device=q.device, dtype=q.dtype)
+        lse = torch.empty(B * Hq * S, device=q.device, dtype=torch.float32)
+        _ext.ext().flash_attn_fwd(q, k, v, o, lse, B, S, Hq, Hkv, float(scale))
+        _count()
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.dims = (B, S, Hq, Hkv, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        B, S, Hq, Hkv, scale = ctx.dims
+        if do.stride(-1) != 1 or do.stride(0) % 8:
+            do = do.contiguous()
+        # dq | dk | dv share one buffer so the fused QKV projection sees a single contiguous gradient
+        dqkv = torch.empty(q.shape[0], (Hq + 2 * Hkv) * 128, device=q.device, dtype=q.dtype)
+        dq = dqkv[:, : Hq * 128]
+        dk = dqkv[:, Hq * 128: (Hq + Hkv) * 128]
+        dv = dqkv[:, (Hq + Hkv) * 128:]
+        delta = torch.empty(B * Hq * S, device=q.device, dtype=torch.float32)
+        _ext.ext().flash_attn_bwd(do, q, k, v, o, lse, dq, dk, dv, delta, B, S, Hq, Hkv, float(scale))
+        _count(2)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def attention(q2d, k2d, v2d, B: int, S: int, Hq: int, Hkv: int, head_dim: int, scale: float | None = None):
+    """Causal GQA attention on ``(B*S, heads*head_dim)`` views; returns ``(B*S, Hq*head_dim)``."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    if use_kernels(q2d) and head_dim == 128:
+        return _FlashAttnFn.apply(q2d, k2d, v2d, B, S, Hq, Hkv, scale)
+    q = q2d.reshape(B, S, Hq, head_dim)
+    k = k2d.reshape(B, S, Hkv, head_dim)
+    v = v2d.reshape(B, S, Hkv, head_dim)
+    return ref.attention(q, k, v, scale).reshape(B * S, Hq * head_dim)
+
+
+# ------------------------------------------------------------------------------------------- SwiGLU
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        out = torch.empty(gate.shape, device=gate.device, dtype=gate.dtype)
+        _ext.ext().swiglu_fwd(gate, up, out)
+        _count()
+        ctx.save_for_backward(gate, up)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        gate, up = ctx.saved_tensors
+        if dout.stride(-1) != 1:
+            dout = dout.contiguous()
+        dgu = torch.empty(gate.shape[0], 2 * gate.shape[1], device=gate.device, dtype=gate.dtype)
+        dgate, dup = dgu[:, : gate.shape[1]], dgu[:, gate.shape[1]:]
+        _ext.ext().swiglu_bwd(dout, gate, up, dgate, dup)
+        _count()
+        return dgate, dup
+
+
+def swiglu(gate, up):
+    """``silu(gate) * up`` on 2-D ``(tokens, I)`` views (either may be a column slice)."""
+    if use_kernels(gate) and gate.dim() == 2 and gate.shape[1] % 8 == 0 and gate.stride(0) % 8 == 0 \
+            and up.stride(0) % 8 == 0:
+        return _SwiGLUFn.apply(gate, up)
+    return ref.swiglu(gate, up)
+
+
+# ------------------------------------------------------------------------------------------- embedding
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table):
+        flat = ids.reshape(-1).contiguous()
+        out = torch.empty(flat.numel(), table.shape[1], device=table.device, dtype=table.dtype)
+        _ext.ext().embedding_fwd(flat, table, out)
+        _count()
+        ctx.save_for_backward(flat)
+        ctx.table = table
+        return out.view(*ids.shape, table.shape[1])
+
+    @staticmethod
+    def backward(ctx, dout):
+        (flat,) = ctx.saved_tensors
+        table = ctx.table
+        d2 = dout.reshape(-1, dout.shape[-1]).contiguous()
+        if isinstance(table, torch.nn.Parameter) and table.grad is not None and table.grad.is_contiguous() \
+                and table.grad.dtype in (torch.bfloat16, torch.float32):
+            _ext.ext().embedding_bwd(flat, d2, table.grad)
+            _count()
+            return None, None
+        dt = torch.zeros(table.shape, device=table.device, dtype=table.dtype)
+        _ext.ext().embedding_bwd(flat, d2, dt)
+        _count(2)
+        return None, dt
+
+
+def embedding(ids, table):
+    if use_kernels(table) and table.shape[1] % 8 == 0:
+        return _EmbeddingFn.apply(ids, table)
+    return torch.nn.functional.embedding(ids, table)
+
+
+# ------------------------------------------------------------------------------------------- lm_head + CE
+class _LinearCrossEntropyFn(torch.autograd.Function):
+    """Token-chunked ``lm_head`` + softmax cross-entropy; logits never exist for more than one chunk.
+
+    The forward pass already produces ``dh`` and ``dW`` (scaled by ``loss_scale / n_valid``, read on
+    the device); the backward pass only rescales by ``g / loss_scale``.
+    """
+
+    @staticmethod
+    def forward(ctx, h, w, labels, ignore_index, chunk, sink, param, loss_scale):
+        e = _ext.ext()
+        T, H = h.shape
+        V = w.shape[0]
+        labels = labels.contiguous()
+        inv = 1.0 / (labels != ignore_index).sum().clamp(min=1).float()
+        loss_sum = torch.zeros((), device=h.device, dtype=torch.float32)
+        count = torch.zeros((), device=h.device, dtype=torch.float32)
+        need_grad = h.requires_grad or w.requires_grad or sink is not None
+        dh = torch.empty_like(h) if need_grad else None
+        direct = loss_scale is not None
+        scale = float(loss_scale) if direct else 1.0
+        target, fresh = None, True
+        if need_grad:
+            if direct and sink is not None:
+                target, fresh = sink.buffer, sink.fresh
+            elif direct and param is not None and param.grad is not None and param.grad.is_contiguous():
+                target, fresh = param.grad, False
+            else:
+                direct = False
+                scale = 1.0
+                target, fresh = torch.empty(V, H, device=h.device, dtype=w.dtype), True
+        logits = torch.empty(min(chunk, T), V, device=h.device, dtype=torch.bfloat16)
+        for t0 in range(0, T, chunk):
+            t1 = min(T, t0 + chunk)
+            lg = logits[: t1 - t0]
+            e.gemm(h[t0:t1], w, lg, None, False, True, 1.0, 0.0, False, 0)
+            e.cross_entropy(lg, labels[t0:t1], loss_sum, count, None, scale, inv, int(ignore_index))
+            _count(2)
+            if need_grad:
+                e.gemm(lg, w, dh[t0:t1], None, False, False, 1.0, 0.0, False, 0)
+                e.gemm(lg, h[t0:t1], target, None if fresh else target, True, False, 1.0, 0.0 if fresh else 1.0, False, 0)
+                fresh = False
+                _count(2)
+        if need_grad and direct and sink is not None:
+            sink.fresh = False
+        ctx.direct = direct
+        ctx.scale = scale
+        if need_grad:
+            ctx.save_for_backward(dh, *([] if direct else [target]))
+        ctx.has_grad = need_grad
+        return loss_sum * inv
+
+    @staticmethod
+    def backward(ctx, g):
+        if not ctx.has_grad:
+            return (None,) * 8
+        saved = ctx.saved_tensors
+        dh = saved[0] * (g / ctx.scale).to(saved[0].dtype)
+        dw = None if ctx.direct else saved[1] * g.to(saved[1].dtype)
+        return dh, dw, None, None, None, None, None, None
+
+
+def linear_cross_entropy(h2d, w, labels, ignore_index: int = -100, chunk: int = 4096, sink: GradSink | None = None,
+                         loss_scale: float | None = None):
+    """Mean cross-entropy of ``h2d @ w.T`` against ``labels`` (``ignore_index`` rows skipped).
+
+    ``loss_scale`` is the factor the caller multiplies the returned loss by before ``backward()``
+    (``1/grad_accumulation``).  When given, the weight gradient is accumulated in place (into
+    ``sink`` or an existing ``w.grad``) during the forward pass, already scaled; without it the
+    gradient flows back through autograd.  The returned loss is always the unscaled mean.
+    """
+    if use_kernels(h2d) and w.dtype == torch.bfloat16:
+        param = w if isinstance(w, torch.nn.Parameter) else None
+        return _LinearCrossEntropyFn.apply(h2d.contiguous(), w, labels, ignore_index, chunk, sink, param, loss_scale)
+    return ref.linear_cross_entropy(h2d, w, labels, ignore_index)

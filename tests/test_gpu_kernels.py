@@ -297,7 +297,7 @@ def test_swiglu_embedding_ce():
     loss = torch.zeros((), device="cuda")
     cnt = torch.zeros((), device="cuda")
     work = logits.clone()
-    e.cross_entropy(work, labels, loss, cnt, None, 1.0, -100)
+    e.cross_entropy(work, labels, loss, cnt, None, 1.0, None, -100)
     assert cnt.item() == (labels != -100).sum().item()
     assert abs(loss.item() - loss_ref.item()) / loss_ref.item() < 2e-3
     _close(work, lr_.grad, atol=2e-3, rtol=2e-2)
