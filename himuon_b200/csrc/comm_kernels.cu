@@ -1,0 +1,214 @@
+// Collectives over peer-mapped (symmetric) memory on NVLink 5 / NVSwitch: plain peer loads and
+// stores, per-block flag handshakes with bounded waits, no NCCL and no multicast loads.
+//
+//   peer_barrier     : stream-ordered barrier between the ranks' GPUs (one tiny launch)
+//   allreduce_symm   : one-launch two-shot all-reduce (reduce-scatter by peer loads, all-gather by
+//                      peer stores) with the average / cast fused; replaces the DDP reducer's
+//                      bucketed NCCL all-reduce (reference: train_ddp.py:90, implicit)
+//   reduce_replicas  : out = scale * sum_r replica_r, the owner-side half of a reduce-scatter for
+//                      optimizers that need a plain `.grad` (HiMuon fuses this step into
+//                      momentum_tile instead)
+//   multi_copy       : one launch that pulls many (peer -> local) segments; the bank all-gather
+//
+// Every wait on a peer flag is bounded: on expiry the kernel records status 6 and returns, so a
+// missing rank surfaces as an error on the host instead of a hung GPU.
+#include "himuon.h"
+#include "sm100_common.cuh"
+
+namespace himuon {
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Waits until *flag >= target.  Returns false after `limit_ns` (status code 6 recorded).
+__device__ __forceinline__ bool wait_flag_ge(const int* flag, int target, unsigned long long limit_ns, int* status) {
+  if (ld_acquire_sys(flag) >= target) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (ld_acquire_sys(flag) < target) {
+    if ((++spins & 0x3F) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        atomicCAS(status, 0, 6);
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+  return true;
+}
+
+// Handshake of block `slot` with the same block index on every peer.
+//   flags[r]  : rank r's flag array (peer-mapped); entry [slot*8 + src] is written by rank `src`
+//   epoch     : this rank's private counter for `slot`, advanced here (graph-replay safe)
+__device__ __forceinline__ bool block_handshake(CommPeers peers, int slot, int* epoch_local, int which, bool* ok_shared) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const int e = ++epoch_local[slot * 2 + which];
+    bool ok = true;
+    for (int r = 0; r < peers.world; ++r)
+      st_release_sys(peers.flags[r] + (which * kCommMaxBlocks + slot) * 8 + peers.rank, e);
+    for (int r = 0; r < peers.world && ok; ++r)
+      ok = wait_flag_ge(peers.flags[peers.rank] + (which * kCommMaxBlocks + slot) * 8 + r, e, peers.limit_ns, peers.status);
+    *ok_shared = ok;
+  }
+  __syncthreads();
+  return *ok_shared;
+}
+
+__global__ void peer_barrier_kernel(CommPeers peers, int* epoch_local) {
+  __shared__ bool ok;
+  block_handshake(peers, kCommMaxBlocks - 1, epoch_local, 0, &ok);
+}
+
+void peer_barrier(const CommPeers& peers, int* epoch_local, cudaStream_t s) {
+  if (peers.world <= 1) return;
+  peer_barrier_kernel<<<1, 32, 0, s>>>(peers, epoch_local);
+}
+
+// ------------------------------------------------------------------------------------------------ all-reduce
+template <typename T>
+__global__ void __launch_bounds__(512)
+allreduce_symm_kernel(CommPeers peers, CommBufs bufs, long long n_elems, float scale, int* epoch_local) {
+  __shared__ bool ok;
+  constexpr int VEC = 16 / sizeof(T);
+  const int world = peers.world, rank = peers.rank;
+  if (!block_handshake(peers, blockIdx.x, epoch_local, 0, &ok)) return;
+  const long long n_vec = n_elems / VEC;                       // n_elems is padded to VEC * world by the caller
+  const long long per_rank = n_vec / world;
+  const long long v0 = per_rank * rank;
+  for (long long v = v0 + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < v0 + per_rank;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int r = 0; r < world; ++r) {
+      const uint4 x = reinterpret_cast<const uint4*>(bufs.ptr[r])[v];
+      const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+      if (sizeof(T) == 2) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { acc[2 * q] += bf16_lo(w[q]); acc[2 * q + 1] += bf16_hi(w[q]); }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[q] += __uint_as_float(w[q]);
+      }
+    }
+    uint4 o;
+    if (sizeof(T) == 2) {
+      o.x = pack_bf16x2(acc[0] * scale, acc[1] * scale); o.y = pack_bf16x2(acc[2] * scale, acc[3] * scale);
+      o.z = pack_bf16x2(acc[4] * scale, acc[5] * scale); o.w = pack_bf16x2(acc[6] * scale, acc[7] * scale);
+    } else {
+      o.x = __float_as_uint(acc[0] * scale); o.y = __float_as_uint(acc[1] * scale);
+      o.z = __float_as_uint(acc[2] * scale); o.w = __float_as_uint(acc[3] * scale);
+    }
+    for (int r = 0; r < world; ++r) reinterpret_cast<uint4*>(bufs.ptr[(rank + r) % world])[v] = o;
+  }
+  block_handshake(peers, blockIdx.x, epoch_local, 1, &ok);
+}
+
+void allreduce_symm(const CommPeers& peers, const CommBufs& bufs, long long n_elems, int is_fp32, float scale,
+                    int* epoch_local, int max_blocks, cudaStream_t s) {
+  if (n_elems <= 0) return;
+  const int vec = is_fp32 ? 4 : 8;
+  if (n_elems % (static_cast<long long>(vec) * peers.world))
+    throw std::runtime_error("himuon allreduce: element count must be a multiple of (16 bytes * world size)");
+  const long long per_rank_vec = n_elems / vec / peers.world;
+  long long blocks = (per_rank_vec + 511) / 512;
+  const int cap = max_blocks > 0 ? max_blocks : num_sms();
+  if (blocks > cap) blocks = cap;
+  if (blocks > kCommMaxBlocks - 1) blocks = kCommMaxBlocks - 1;
+  if (blocks < 1) blocks = 1;
+  if (is_fp32)
+    allreduce_symm_kernel<float><<<static_cast<int>(blocks), 512, 0, s>>>(peers, bufs, n_elems, scale, epoch_local);
+  else
+    allreduce_symm_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 512, 0, s>>>(peers, bufs, n_elems, scale, epoch_local);
+}
+
+// ------------------------------------------------------------------------------------------------ reduce replicas
+template <typename T>
+__global__ void __launch_bounds__(512)
+reduce_replicas_kernel(CommBufs srcs, int n_src, T* __restrict__ out, long long n_elems, float scale) {
+  constexpr int VEC = 16 / sizeof(T);
+  const long long n_vec = n_elems / VEC;
+  for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < n_vec;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int r = 0; r < n_src; ++r) {
+      const uint4 x = reinterpret_cast<const uint4*>(srcs.ptr[r])[v];
+      const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+      if (sizeof(T) == 2) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { acc[2 * q] += bf16_lo(w[q]); acc[2 * q + 1] += bf16_hi(w[q]); }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[q] += __uint_as_float(w[q]);
+      }
+    }
+    uint4 o;
+    if (sizeof(T) == 2) {
+      o.x = pack_bf16x2(acc[0] * scale, acc[1] * scale); o.y = pack_bf16x2(acc[2] * scale, acc[3] * scale);
+      o.z = pack_bf16x2(acc[4] * scale, acc[5] * scale); o.w = pack_bf16x2(acc[6] * scale, acc[7] * scale);
+    } else {
+      o.x = __float_as_uint(acc[0] * scale); o.y = __float_as_uint(acc[1] * scale);
+      o.z = __float_as_uint(acc[2] * scale); o.w = __float_as_uint(acc[3] * scale);
+    }
+    reinterpret_cast<uint4*>(out)[v] = o;
+  }
+}
+
+void reduce_replicas(const CommBufs& srcs, int n_src, void* out, long long n_elems, int is_fp32, float scale,
+                     cudaStream_t s) {
+  if (n_elems <= 0) return;
+  const int vec = is_fp32 ? 4 : 8;
+  if (n_elems % vec) throw std::runtime_error("himuon reduce_replicas: element count must be a multiple of 16 bytes");
+  long long blocks = (n_elems / vec + 511) / 512;
+  const long long cap = static_cast<long long>(num_sms()) * 2;
+  if (blocks > cap) blocks = cap;
+  if (is_fp32)
+    reduce_replicas_kernel<float><<<static_cast<int>(blocks), 512, 0, s>>>(srcs, n_src, reinterpret_cast<float*>(out), n_elems, scale);
+  else
+    reduce_replicas_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 512, 0, s>>>(srcs, n_src, reinterpret_cast<__nv_bfloat16*>(out), n_elems, scale);
+}
+
+// ------------------------------------------------------------------------------------------------ multi copy
+constexpr long long kCopyUnit = 1 << 16;   // bytes per work unit
+
+__global__ void __launch_bounds__(512)
+multi_copy_kernel(const CopySeg* __restrict__ segs, int n_segs, long long total_units) {
+  for (long long unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+    int lo = 0, hi = n_segs - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (segs[mid].unit_begin <= unit) lo = mid; else hi = mid - 1;
+    }
+    const CopySeg sg = segs[lo];
+    const long long off = (unit - sg.unit_begin) * kCopyUnit;
+    const long long len = min(kCopyUnit, sg.bytes - off);
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(sg.src) + off);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(sg.dst) + off);
+    const int nv = static_cast<int>(len >> 4);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+long long multi_copy_units(long long bytes) { return (bytes + kCopyUnit - 1) / kCopyUnit; }
+
+void multi_copy(const CopySeg* segs_dev, int n_segs, long long total_units, int max_blocks, cudaStream_t s) {
+  if (total_units <= 0) return;
+  long long blocks = total_units;
+  const long long cap = max_blocks > 0 ? max_blocks : num_sms();
+  if (blocks > cap) blocks = cap;
+  multi_copy_kernel<<<static_cast<int>(blocks), 512, 0, s>>>(segs_dev, n_segs, total_units);
+}
+
+}  // namespace himuon

@@ -131,6 +131,27 @@ struct AttnArgs {
 void flash_attn_fwd(const AttnArgs& a, cudaStream_t s);
 void flash_attn_bwd(const AttnArgs& a, cudaStream_t s);
 
+// ---------------------------------------------------------------- collectives over peer-mapped memory
+constexpr int kCommMaxBlocks = 256;
+// Flag area of one rank: int[2][kCommMaxBlocks][8] (phase, block slot, writing rank), zero-initialised.
+constexpr long long kCommFlagBytes = 2LL * kCommMaxBlocks * 8 * sizeof(int);
+struct CommPeers {
+  int* flags[kMaxSrc];            // every rank's flag area as mapped into this process
+  int world, rank;
+  unsigned long long limit_ns;    // bound of each wait on a peer flag
+  int* status;                    // status word (code 6 on expiry)
+};
+struct CommBufs { void* ptr[kMaxSrc]; };
+struct CopySeg { const void* src; void* dst; long long bytes; long long unit_begin; };
+// epoch_local: int[2*kCommMaxBlocks] private to this rank, zero-initialised, advanced by the kernels.
+void peer_barrier(const CommPeers& peers, int* epoch_local, cudaStream_t s);
+void allreduce_symm(const CommPeers& peers, const CommBufs& bufs, long long n_elems, int is_fp32, float scale,
+                    int* epoch_local, int max_blocks, cudaStream_t s);
+void reduce_replicas(const CommBufs& srcs, int n_src, void* out, long long n_elems, int is_fp32, float scale,
+                     cudaStream_t s);
+long long multi_copy_units(long long bytes);
+void multi_copy(const CopySeg* segs_dev, int n_segs, long long total_units, int max_blocks, cudaStream_t s);
+
 // ---------------------------------------------------------------- fused tile-resident NS5
 // Five quintic Newton-Schulz iterations on (B, m, n) bf16 tiles with m <= n, m <= 128, n <= 128*... kept in
 // shared memory for the whole computation (see ns5_sm100.cu).

@@ -1,4 +1,122 @@
+// Symmetric memory runtime: one cudaMalloc'd heap per rank, shared with the other ranks of the
+// node through CUDA IPC handles, plus the communicator object that launches the collective kernels
+// of comm_kernels.cu over it.  Handle exchange itself happens in Python over torch.distributed.
 #include "symm.h"
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime.h>
+#include <torch/extension.h>
+
+#include <cstring>
+#include <vector>
+
+#include "himuon.h"
+
+namespace py = pybind11;
+
 namespace himuon {
-void bind_symm(pybind11::module_& m) { (void)m; }
+
+static void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string("himuon symm: ") + what + ": " + cudaGetErrorString(e));
+}
+
+static py::tuple symm_alloc(int64_t nbytes) {
+  void* p = nullptr;
+  check(cudaMalloc(&p, static_cast<size_t>(nbytes)), "cudaMalloc");
+  check(cudaMemset(p, 0, static_cast<size_t>(nbytes)), "cudaMemset");
+  cudaIpcMemHandle_t h;
+  check(cudaIpcGetMemHandle(&h, p), "cudaIpcGetMemHandle");
+  return py::make_tuple(reinterpret_cast<int64_t>(p), py::bytes(reinterpret_cast<const char*>(&h), sizeof(h)));
+}
+
+static int64_t symm_open(const py::bytes& handle) {
+  std::string s = handle;
+  if (s.size() != sizeof(cudaIpcMemHandle_t)) throw std::runtime_error("himuon symm: malformed IPC handle");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, s.data(), sizeof(h));
+  void* p = nullptr;
+  check(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+  return reinterpret_cast<int64_t>(p);
+}
+
+static void symm_close(int64_t ptr) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); }
+static void symm_free(int64_t ptr) { cudaFree(reinterpret_cast<void*>(ptr)); }
+
+// A tensor over raw device memory that this module does not own (heap slices, peer mappings).
+static at::Tensor tensor_view(int64_t ptr, std::vector<int64_t> shape, const std::string& dtype, int64_t device) {
+  at::ScalarType st = dtype == "bf16" ? at::kBFloat16 : dtype == "f32" ? at::kFloat : dtype == "i32" ? at::kInt
+                    : dtype == "u8" ? at::kByte : at::kLong;
+  auto opts = at::TensorOptions().dtype(st).device(at::kCUDA, static_cast<c10::DeviceIndex>(device));
+  return at::from_blob(reinterpret_cast<void*>(ptr), shape, [](void*) {}, opts);
+}
+
+class Comm {
+ public:
+  Comm(int rank, int world, std::vector<int64_t> heap_ptrs, double timeout_s) : heaps_(std::move(heap_ptrs)) {
+    if (world < 1 || world > kMaxSrc || static_cast<int>(heaps_.size()) != world)
+      throw std::runtime_error("himuon symm: world size must be 1..8 with one heap pointer per rank");
+    peers_.world = world;
+    peers_.rank = rank;
+    for (int r = 0; r < kMaxSrc; ++r) peers_.flags[r] = r < world ? reinterpret_cast<int*>(heaps_[r]) : nullptr;
+    set_timeout(timeout_s);
+    peers_.status = status_word_ptr();
+    check(cudaMalloc(&epoch_, 2 * kCommMaxBlocks * sizeof(int)), "cudaMalloc(epoch)");
+    check(cudaMemset(epoch_, 0, 2 * kCommMaxBlocks * sizeof(int)), "cudaMemset(epoch)");
+  }
+  ~Comm() {
+    if (epoch_) cudaFree(epoch_);
+  }
+  void set_timeout(double s) { peers_.limit_ns = static_cast<unsigned long long>(s * 1e9); }
+  int64_t peer_ptr(int r) const { return heaps_.at(r); }
+  static int64_t flag_bytes() { return kCommFlagBytes; }
+
+  void barrier() { peer_barrier(peers_, epoch_, at::cuda::getCurrentCUDAStream().stream()); }
+
+  // In-place all-reduce of the same heap region on every rank.
+  void allreduce(int64_t offset_bytes, int64_t n_elems, bool fp32, double scale, int64_t max_blocks) {
+    if (peers_.world == 1) return;
+    CommBufs b{};
+    for (int r = 0; r < peers_.world; ++r) b.ptr[r] = reinterpret_cast<char*>(heaps_[r]) + offset_bytes;
+    allreduce_symm(peers_, b, n_elems, fp32 ? 1 : 0, static_cast<float>(scale), epoch_, static_cast<int>(max_blocks),
+                   at::cuda::getCurrentCUDAStream().stream());
+  }
+  // out = scale * sum over ranks of the heap region at offset_bytes.
+  void reduce_to(int64_t offset_bytes, at::Tensor out, double scale) {
+    TORCH_CHECK(out.is_cuda() && out.is_contiguous(), "himuon reduce_to: contiguous CUDA output expected");
+    CommBufs b{};
+    for (int r = 0; r < peers_.world; ++r) b.ptr[r] = reinterpret_cast<char*>(heaps_[r]) + offset_bytes;
+    reduce_replicas(b, peers_.world, out.data_ptr(), out.numel(), out.scalar_type() == at::kFloat ? 1 : 0,
+                    static_cast<float>(scale), at::cuda::getCurrentCUDAStream().stream());
+  }
+  void copy_segments(const at::Tensor& segs, int64_t n_segs, int64_t total_units, int64_t max_blocks) {
+    TORCH_CHECK(segs.is_cuda() && segs.numel() >= n_segs * (int64_t)sizeof(CopySeg), "himuon copy_segments: table too small");
+    multi_copy(reinterpret_cast<const CopySeg*>(segs.data_ptr()), static_cast<int>(n_segs), total_units,
+               static_cast<int>(max_blocks), at::cuda::getCurrentCUDAStream().stream());
+  }
+
+ private:
+  std::vector<int64_t> heaps_;
+  CommPeers peers_{};
+  int* epoch_ = nullptr;
+};
+
+void bind_symm(py::module_& m) {
+  m.def("symm_alloc", &symm_alloc);
+  m.def("symm_open", &symm_open);
+  m.def("symm_close", &symm_close);
+  m.def("symm_free", &symm_free);
+  m.def("tensor_view", &tensor_view);
+  m.def("multi_copy_units", [](int64_t bytes) { return multi_copy_units(bytes); });
+  py::class_<Comm>(m, "Comm")
+      .def(py::init<int, int, std::vector<int64_t>, double>())
+      .def("set_timeout", &Comm::set_timeout)
+      .def("peer_ptr", &Comm::peer_ptr)
+      .def_static("flag_bytes", &Comm::flag_bytes)
+      .def("barrier", &Comm::barrier)
+      .def("allreduce", &Comm::allreduce)
+      .def("reduce_to", &Comm::reduce_to)
+      .def("copy_segments", &Comm::copy_segments);
+}
+
 }  // namespace himuon

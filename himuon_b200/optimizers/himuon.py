@@ -105,6 +105,7 @@ class HiMuon(Optimizer):
         self._ns_workspace = ns_ops.NSWorkspace()
         self._ptr_signature = None
         self._graph_stats = dict(self._last_step_stats)
+        self._graph_launches = 0
         if self._cuda_graph_enabled and any(_is_dtensor(p) for g in self.param_groups for p in g["params"]):
             warnings.warn(
                 "HiMuon on DTensor parameters with cuda_graph=True: the graph's memory pool and the FSDP "
@@ -217,7 +218,10 @@ class HiMuon(Optimizer):
                         f"local ndim={lp.ndim}. Wrap the model with wrap_with_banks() before sharding.")
                 if lp.ndim == 3:
                     N, H, W = lp.shape
+                    skip = getattr(p, "_hm_skip_slots", ())
                     for n in range(N):
+                        if n in skip:      # padding slot of a bank: zero forever, nothing to orthogonalise
+                            continue
                         m = _Matrix(p, n, gi, H, W)
                         if th >= H and tw >= W:
                             m.full, m.tile, m.block = False, (H, W), (H, W)
@@ -524,20 +528,27 @@ class HiMuon(Optimizer):
             self._ptr_signature = sig
         self._refresh_hyper()
         if self._cuda_graph is not None:
+            from ..ops import _count
             self._cuda_graph.replay()
+            _count(self._graph_launches)      # the kernels recorded in the graph run again on every replay
             self._graph_step_count += 1
             self._last_step_stats = dict(self._graph_stats, ns_gpu_ms=0.0)
             return
         use_graph = self._cuda_graph_enabled
         if use_graph and self._graph_step_count >= self._cuda_graph_warmup:
+            from ..ops import _count, launch_count
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             self._in_graph_region = True
+            before = launch_count()
             try:
                 with torch.cuda.graph(graph):
                     stats = self._launch_all()
             finally:
                 self._in_graph_region = False
+            self._graph_launches = launch_count() - before
+            _count(-self._graph_launches)     # capture records the kernels without running them
+            _count(self._graph_launches)      # ... and the replay below runs them once
             self._cuda_graph = graph
             self._graph_stats = stats
             graph.replay()

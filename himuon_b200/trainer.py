@@ -278,6 +278,8 @@ def run_training(args, mode: str) -> dict:
         scheduler = wsd_schedule(optimizer, args.num_warmup_steps, 0, args.num_decay_steps, args.min_lr_ratio)
     else:
         scheduler = cosine_with_warmup(optimizer, args.num_warmup_steps, args.num_training_steps)
+    if mode == "fsdp":
+        engine.attach_optimizer(optimizer)
     if logger is not None:
         logger.log_optimizer_source(optimizer)
     apply_reconfigure = make_apply_reconfigure(optimizer, parse_reconfigure_schedule(args.reconfigure_schedule), log)
