@@ -400,6 +400,12 @@ class HiMuon(Optimizer):
             th, tw, full, gdtype = bucket["bucket_key"]
             ms: list[_Matrix] = bucket["_entries"]
             B_total = bucket["B_total"]
+            if th % 8 or tw % 8:
+                # TMA rows are 16 bytes: a tile side that is not a multiple of 8 is padded with zeros, which
+                # leaves the iteration unchanged, but only when the tile is the whole matrix.
+                if any(m.R != 1 or m.C != 1 for m in ms):
+                    raise ValueError(f"HiMuon on CUDA needs tile sides that are multiples of 8, got ({th}, {tw})")
+                th, tw = -(-th // 8) * 8, -(-tw // 8) * 8
             buf = self._ensure_concat_buffer(bucket["bucket_key"], B_total, th, tw, device, torch.bfloat16)
             by_cfg: dict[tuple, list[_Matrix]] = {}
             tile_base = 0

@@ -1,0 +1,152 @@
+"""HiMuon on the GPU kernels: NS dispatcher against the PyTorch oracle, smoke over dtype x tile, chunk-size
+invariance, eager == graph, reconfigure invalidation, flat memory after capture, GPU == CPU optimizer step.
+Mirrors the reference's tests/integration/test_himuon_{smoke,self_consistency,reconfigure,memory,dispatch}.py."""
+
+import pytest
+import torch
+
+from helpers import make_linear_model, seed_grads
+
+pytestmark = pytest.mark.gpu
+
+
+def _well_conditioned(B, m, n, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, m, n, generator=g)
+    U, _, Vh = torch.linalg.svd(x, full_matrices=False)
+    return (U * torch.linspace(0.8, 1.2, min(m, n))) @ Vh
+
+
+@pytest.mark.parametrize("shape", [(3, 512, 512), (2, 256, 512), (2, 512, 256), (5, 128, 128), (2, 768, 513),
+                                   (1, 1024, 1024), (4, 64, 64), (2, 16, 1024)])
+def test_newton_schulz_dispatcher_matches_oracle(shape):
+    from himuon_b200 import ops
+    from himuon_b200.ops import ns as ns_ops
+    from himuon_b200.ops import reference as ref
+
+    x = _well_conditioned(*shape).cuda().bfloat16()
+    out = ns_ops.newton_schulz(x, 5)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = ref.newton_schulz(x.cpu(), 5).float()
+    err = (out.float().cpu() - want).abs()
+    assert out.shape == x.shape and out.dtype == x.dtype
+    assert (err > 4e-2 + 4e-2 * want.abs()).float().mean() < 1e-3, err.max()
+    x2d = x[0]
+    assert torch.allclose(ns_ops.newton_schulz(x2d, 5).float(), out[0].float(), atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("tile", [128, 256, (128, 256), 1000000])
+def test_smoke_finite_and_changed(dtype, tile):
+    from himuon_b200.optimizers import HiMuon
+
+    model = make_linear_model([(512, 512), (768, 513 if dtype == torch.float32 else 520), (64, 64), (256, 1024)], dtype, "cuda")
+    opt = HiMuon(model.parameters(), tile_size=tile, cuda_graph=False)
+    before = [p.detach().clone() for p in model.parameters()]
+    for s in range(2):
+        seed_grads(model, s)
+        opt.step()
+    for p, b in zip(model.parameters(), before):
+        assert torch.isfinite(p).all() and not torch.equal(p, b)
+
+
+def _run(b_hw=None, cuda_graph=False, steps=5, dtype=torch.bfloat16):
+    from himuon_b200.optimizers import HiMuon
+
+    torch.manual_seed(0)
+    model = make_linear_model([(512, 768), (300, 520), (128, 128)], dtype, "cuda")
+    bias = torch.nn.Parameter(torch.zeros(64, device="cuda", dtype=dtype))
+    opt = HiMuon([{"params": list(model.parameters())}, {"params": [bias], "use_muon": False, "lr": 1e-3}],
+                 tile_size=128, b_hw=b_hw, cuda_graph=cuda_graph, cuda_graph_warmup=2)
+    seed_grads(model, 0)
+    bias.grad = torch.zeros_like(bias)
+    for s in range(steps):
+        seed_grads(model, s)                      # in place: addresses stay stable for the graph
+        bias.grad.copy_(torch.full_like(bias, 0.1 * (s + 1)))
+        opt.step()
+    torch.cuda.synchronize()
+    return [p.detach().float().cpu() for p in list(model.parameters()) + [bias]], opt
+
+
+def test_chunk_size_invariance_and_eager_equals_graph():
+    base, _ = _run()
+    chunked, opt_c = _run(b_hw=5)
+    assert opt_c.xlayer_plan()[0]["n_calls"] > 1
+    graph, opt_g = _run(cuda_graph=True)
+    assert opt_g._cuda_graph is not None and opt_g._graph_step_count == 5
+    for a, b, c in zip(base, chunked, graph):
+        assert torch.allclose(a, b, atol=1e-2, rtol=1e-2)
+        assert torch.allclose(a, c, atol=1e-2, rtol=1e-2)
+
+
+def test_gpu_step_matches_cpu_step():
+    from himuon_b200.optimizers import HiMuon
+
+    gpu, _ = _run(steps=3, dtype=torch.float32)
+    torch.manual_seed(0)
+    model = make_linear_model([(512, 768), (300, 520), (128, 128)])
+    bias = torch.nn.Parameter(torch.zeros(64))
+    opt = HiMuon([{"params": list(model.parameters())}, {"params": [bias], "use_muon": False, "lr": 1e-3}],
+                 tile_size=128, cuda_graph=False)
+    for s in range(3):
+        seed_grads(model, s)
+        bias.grad = torch.full_like(bias, 0.1 * (s + 1))
+        opt.step()
+    for a, p in zip(gpu, list(model.parameters()) + [bias]):
+        assert torch.allclose(a, p.detach(), atol=3e-3, rtol=1e-2), (a - p.detach()).abs().max()
+
+
+def test_reconfigure_in_graph_mode_recaptures():
+    from himuon_b200.optimizers import HiMuon
+
+    model = make_linear_model([(512, 512), (256, 512)], torch.bfloat16, "cuda")
+    opt = HiMuon(model.parameters(), tile_size=256, cuda_graph=True, cuda_graph_warmup=1)
+    seed_grads(model, 0)
+    for s in range(3):
+        seed_grads(model, s)
+        opt.step()
+    assert opt._cuda_graph is not None
+    opt.reconfigure(tile_size=128)
+    assert opt._cuda_graph is None and opt._cached_plan is None and opt._graph_step_count == 0
+    for s in range(3):
+        seed_grads(model, s)
+        opt.step()
+    assert opt._cuda_graph is not None and opt.xlayer_plan()[0]["bucket_key"][:2] == (128, 128)
+    assert all(torch.isfinite(p).all() for p in model.parameters())
+
+
+def test_memory_is_flat_after_capture():
+    from himuon_b200.optimizers import HiMuon
+
+    model = make_linear_model([(1024, 1024)] * 4, torch.bfloat16, "cuda")
+    opt = HiMuon(model.parameters(), tile_size=512, cuda_graph=True, cuda_graph_warmup=2)
+    seed_grads(model, 0)
+    for s in range(4):
+        seed_grads(model, s)
+        opt.step()
+    torch.cuda.synchronize()
+    base = torch.cuda.memory_allocated()
+    for s in range(10):
+        seed_grads(model, s)
+        opt.step()
+    torch.cuda.synchronize()
+    assert abs(torch.cuda.memory_allocated() - base) <= 0.01 * base
+
+
+def test_lr_schedule_takes_effect_without_recapture():
+    from himuon_b200.optimizers import HiMuon
+
+    model = make_linear_model([(256, 256)], torch.float32, "cuda")
+    opt = HiMuon(model.parameters(), tile_size=128, cuda_graph=True, cuda_graph_warmup=1, weight_decay=0.0)
+    seed_grads(model, 0)
+    for s in range(3):
+        opt.step()
+    graph = opt._cuda_graph
+    p = next(model.parameters())
+    for g in opt.param_groups:
+        g["lr"] = 0.0
+    before = p.detach().clone()
+    opt.step()
+    torch.cuda.synchronize()
+    assert opt._cuda_graph is graph and torch.equal(p, before)      # lr 0 -> no change, same captured graph
