@@ -19,6 +19,7 @@ CUDA_SOURCES = [
     "attention_sm100.cu",
     "ns5_sm100.cu",
     "comm_kernels.cu",
+    "rmsnorm_bwd_noalloc.cu",
 ]
 CPP_SOURCES = ["bindings.cpp", "symm.cpp"]
 
