@@ -14,6 +14,8 @@
 #include "sm100_common.cuh"
 #include "tma_host.h"
 
+#include <cstdlib>
+
 namespace himuon {
 
 __device__ int g_status_word = 0;
@@ -27,15 +29,119 @@ struct GemmDev {
   int out_fp32;     // 1: C/aux are fp32, 0: bf16
   int round_acc;    // 1: round alpha*acc to bf16 before adding beta*aux
   int tiles_m, tiles_n, kblocks;
+  int tma_store;    // 1: epilogue goes through shared-memory slabs and TMA stores (needs 16-byte aligned C rows)
   int* status;
 };
 
 constexpr int BM = 128;
 constexpr int BK = 64;
+constexpr uint32_t SLAB_BYTES = BM * 128;   // one staging slab: 128 rows x 128 bytes (64 bf16 or 32 fp32 columns)
+
+// Loads the 128 bytes of `aux` that belong to this thread's row of a slab (zeros when there is no aux).
+template <bool OUT_FP32>
+__device__ __forceinline__ void load_aux_slab(const void* aux, long long elem_off, bool row_ok, int valid_cols,
+                                              uint4 (&x)[8]) {
+  constexpr int SW = OUT_FP32 ? 32 : 64;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) x[j] = make_uint4(0, 0, 0, 0);
+  if (aux == nullptr || !row_ok || valid_cols <= 0) return;
+  if (OUT_FP32) {
+    const float* ptr = reinterpret_cast<const float*>(aux) + elem_off;
+    if (valid_cols >= SW && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = reinterpret_cast<const uint4*>(ptr)[j];
+    } else {
+      uint32_t* w = reinterpret_cast<uint32_t*>(x);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (j < valid_cols) w[j] = __float_as_uint(ptr[j]);
+    }
+  } else {
+    const __nv_bfloat16* ptr = reinterpret_cast<const __nv_bfloat16*>(aux) + elem_off;
+    if (valid_cols >= SW && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = reinterpret_cast<const uint4*>(ptr)[j];
+    } else {
+      uint32_t* w = reinterpret_cast<uint32_t*>(x);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float lo = (2 * j < valid_cols) ? __bfloat162float(ptr[2 * j]) : 0.f;
+        const float hi = (2 * j + 1 < valid_cols) ? __bfloat162float(ptr[2 * j + 1]) : 0.f;
+        w[j] = pack_bf16x2(lo, hi);
+      }
+    }
+  }
+}
+
+// Epilogue of one accumulator tile through swizzled shared-memory slabs and TMA stores.  Called by the 128
+// epilogue threads together.  `slab_seq` numbers the slabs this CTA has stored so far (selects the staging buffer).
+template <int BN, bool OUT_FP32>
+__device__ __forceinline__ void epilogue_tile_tma(const CUtensorMap* tmC, uint8_t* sC, uint32_t t_row, int row_in_tile,
+                                                  int m0, int n0, int b, const void* aux, long long aux_row_off,
+                                                  int M, int N, float alpha, float beta, int round_acc,
+                                                  uint32_t& slab_seq, bool issuer) {
+  constexpr int SW = OUT_FP32 ? 32 : 64;
+  constexpr int SLABS = BN / SW;
+  const bool row_ok = (m0 + row_in_tile) < M;
+  uint4 xa[8], xn[8];
+  load_aux_slab<OUT_FP32>(aux, aux_row_off + n0, row_ok, N - n0, xa);
+#pragma unroll 1
+  for (int sl = 0; sl < SLABS; ++sl) {
+    const int col = n0 + sl * SW;
+    if (col >= N) break;                                   // uniform over the 128 threads
+    if (sl + 1 < SLABS) load_aux_slab<OUT_FP32>(aux, aux_row_off + col + SW, row_ok, N - col - SW, xn);
+    named_barrier(1, 128);                                 // the staging buffer is free (issuer waited on its reads)
+    uint8_t* buf = sC + (slab_seq & 1) * SLAB_BYTES;
+    uint8_t* my_row = buf + row_in_tile * 128;
+#pragma unroll
+    for (int ch = 0; ch < SW / 32; ++ch) {
+      uint32_t v[32];
+      tmem_ld32(t_row + sl * SW + ch * 32, v);
+      tmem_ld_wait();
+      if (OUT_FP32) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 o;
+          o.x = alpha * __uint_as_float(v[4 * j + 0]) + beta * __uint_as_float(xa[j].x);
+          o.y = alpha * __uint_as_float(v[4 * j + 1]) + beta * __uint_as_float(xa[j].y);
+          o.z = alpha * __uint_as_float(v[4 * j + 2]) + beta * __uint_as_float(xa[j].z);
+          o.w = alpha * __uint_as_float(v[4 * j + 3]) + beta * __uint_as_float(xa[j].w);
+          *reinterpret_cast<float4*>(my_row + ((j ^ (row_in_tile & 7)) << 4)) = o;
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 e = xa[ch * 4 + q];
+          const uint32_t ew[4] = {e.x, e.y, e.z, e.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            float f0 = alpha * __uint_as_float(v[8 * q + 2 * t]);
+            float f1 = alpha * __uint_as_float(v[8 * q + 2 * t + 1]);
+            if (round_acc) { f0 = round_bf16(f0); f1 = round_bf16(f1); }
+            o[t] = pack_bf16x2(f0 + beta * bf16_lo(ew[t]), f1 + beta * bf16_hi(ew[t]));
+          }
+          const int j = ch * 4 + q;
+          *reinterpret_cast<uint4*>(my_row + ((j ^ (row_in_tile & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    named_barrier(2, 128);                                 // the slab is complete
+    if (issuer) {
+      tma_store_3d(tmC, buf, col, m0, b);
+      tma_store_commit();
+      tma_store_wait_read<1>();                            // the other buffer's previous store has drained
+    }
+    ++slab_seq;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) xa[j] = xn[j];
+  }
+}
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(256, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmDev p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, GemmDev p) {
   constexpr uint32_t A_BYTES = BM * BK * 2;
   constexpr uint32_t B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -43,7 +149,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align_up_1024(smem_raw);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* sC = smem + STAGES * STAGE_BYTES;                      // two staging slabs for the TMA-store epilogue
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sC + 2 * SLAB_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
   uint64_t* tfull = bars + 2 * STAGES;
@@ -151,6 +258,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int ew = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t slab_seq = 0;
+    const bool issuer = (threadIdx.x == 128);
+    if (issuer && p.tma_store) tma_prefetch_desc(&tmC);
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const int b = tile / tiles_per_batch;
       const int r = tile - b * tiles_per_batch;
@@ -158,6 +268,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int nt = r / p.tiles_m;
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, p.status, 3)) break;
       tc_fence_after();
+      if (p.tma_store) {
+        const int row_in_tile = ew * 32 + lane;
+        const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(acc * BN);
+        const long long aux_row = static_cast<long long>(b) * p.strideAux + static_cast<long long>(mt * BM + row_in_tile) * p.ldaux;
+        if (p.out_fp32)
+          epilogue_tile_tma<BN, true>(&tmC, sC, t_acc, row_in_tile, mt * BM, nt * BN, b, p.aux, aux_row, p.M, p.N,
+                                      p.alpha, p.beta, p.round_acc, slab_seq, issuer);
+        else
+          epilogue_tile_tma<BN, false>(&tmC, sC, t_acc, row_in_tile, mt * BM, nt * BN, b, p.aux, aux_row, p.M, p.N,
+                                       p.alpha, p.beta, p.round_acc, slab_seq, issuer);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+        continue;
+      }
       const int row = mt * BM + ew * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(acc * BN);
@@ -253,6 +380,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    if (issuer && p.tma_store) tma_store_wait_read<0>();   // no store may still be reading shared memory at exit
   }
 
   tc_fence_before();
@@ -263,10 +391,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// Developer knobs read once from the environment: HIMUON_GEMM_EPILOGUE=direct, HIMUON_GEMM_BN=128|192|256.
+struct GemmTuning { bool force_direct = false; int force_bn = 0; };
+static const GemmTuning& tuning() {
+  static GemmTuning t = [] {
+    GemmTuning g;
+    const char* e = getenv("HIMUON_GEMM_EPILOGUE");
+    if (e && std::string(e) == "direct") g.force_direct = true;
+    const char* b = getenv("HIMUON_GEMM_BN");
+    if (b) g.force_bn = atoi(b);
+    return g;
+  }();
+  return t;
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 static void launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * 2;
-  constexpr size_t SMEM = 1024 + STAGES * STAGE_BYTES + 256;
+  constexpr size_t SMEM = 1024 + STAGES * STAGE_BYTES + 2 * SLAB_BYTES + 256;
+  static_assert(SMEM <= 232448, "shared memory budget of one CTA exceeded");
   auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
   static bool attr_done = false;
   if (!attr_done) {
@@ -298,10 +441,24 @@ static void launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   p.tiles_n = (a.N + BN - 1) / BN;
   p.kblocks = (a.K + BK - 1) / BK;
   p.status = status_word_ptr();
+  // C tensor map for the TMA-store epilogue: rows of 128 bytes (64 bf16 / 32 fp32 columns) per slab.
+  const int esz = a.out_fp32 ? 4 : 2;
+  const int row_align = 16 / esz;
+  p.tma_store = (a.ldc % row_align == 0) && (a.batch == 1 || a.strideC % row_align == 0) &&
+                (reinterpret_cast<uintptr_t>(a.C) % 16 == 0) ? 1 : 0;
+  if (tuning().force_direct) p.tma_store = 0;
+  CUtensorMap tmC = tmA;
+  if (p.tma_store) {
+    const uint64_t dimsC[3] = {static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.M), static_cast<uint64_t>(a.batch)};
+    const uint64_t strC[2] = {static_cast<uint64_t>(a.ldc) * esz,
+                              a.batch > 1 ? static_cast<uint64_t>(a.strideC) * esz : static_cast<uint64_t>(a.ldc) * esz * a.M};
+    const uint32_t boxC[3] = {static_cast<uint32_t>(128 / esz), BM, 1};
+    tmC = make_tmap(a.C, 3, dimsC, strC, boxC, esz, true);
+  }
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batch;
   int sms = a.max_ctas > 0 ? a.max_ctas : num_sms();
   const int grid = static_cast<int>(total < sms ? total : sms);
-  kern<<<grid, 256, SMEM, stream>>>(tmA, tmB, p);
+  kern<<<grid, 256, SMEM, stream>>>(tmA, tmB, tmC, p);
 }
 
 int num_sms() {
@@ -316,25 +473,22 @@ int num_sms() {
 void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if (a.M <= 0 || a.N <= 0 || a.batch <= 0) return;
   if (a.K <= 0) throw std::runtime_error("himuon gemm: K must be positive");
-  // Narrow outputs use the 128-wide tile (more tiles, deeper ring); wide ones the 256-wide tile.
-  const long long tiles256 = static_cast<long long>((a.M + BM - 1) / BM) * ((a.N + 255) / 256) * a.batch;
-  const bool bn128 = a.N <= 128 || tiles256 < num_sms();
+  // Tile width.  The main loop is bound by L2 -> shared-memory traffic, so the widest tile (highest arithmetic
+  // intensity) wins even when it costs an extra partial wave; narrow tiles are only for narrow outputs.
+  int best_bn = a.N <= 128 ? 128 : (a.N <= 192 ? 192 : 256);
+  if (tuning().force_bn == 128 || tuning().force_bn == 192 || tuning().force_bn == 256) best_bn = tuning().force_bn;
   const int sel = (a.a_mn ? 2 : 0) | (a.b_mn ? 1 : 0);
-  if (bn128) {
-    switch (sel) {
-      case 0: launch_gemm<128, 6, false, false>(a, stream); break;
-      case 1: launch_gemm<128, 6, false, true>(a, stream); break;
-      case 2: launch_gemm<128, 6, true, false>(a, stream); break;
-      default: launch_gemm<128, 6, true, true>(a, stream); break;
-    }
-  } else {
-    switch (sel) {
-      case 0: launch_gemm<256, 4, false, false>(a, stream); break;
-      case 1: launch_gemm<256, 4, false, true>(a, stream); break;
-      case 2: launch_gemm<256, 4, true, false>(a, stream); break;
-      default: launch_gemm<256, 4, true, true>(a, stream); break;
-    }
+#define HM_LAUNCH(BN_, ST_)                                                        \
+  switch (sel) {                                                                   \
+    case 0: launch_gemm<BN_, ST_, false, false>(a, stream); break;                 \
+    case 1: launch_gemm<BN_, ST_, false, true>(a, stream); break;                  \
+    case 2: launch_gemm<BN_, ST_, true, false>(a, stream); break;                  \
+    default: launch_gemm<BN_, ST_, true, true>(a, stream); break;                  \
   }
+  if (best_bn == 128) { HM_LAUNCH(128, 6) }
+  else if (best_bn == 192) { HM_LAUNCH(192, 4) }
+  else { HM_LAUNCH(256, 4) }
+#undef HM_LAUNCH
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("himuon gemm launch failed: ") + cudaGetErrorString(e));
 }

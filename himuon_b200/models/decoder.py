@@ -32,6 +32,18 @@ class Linear(nn.Linear):
         return y if self.bias is None else y + self.bias
 
 
+def _bank_pair(first: nn.Linear, second: nn.Linear):
+    """When two bias-free projections occupy neighbouring slots ``2i, 2i+1`` of one parameter bank that a
+    sharding engine serves, returns a callable computing both with a single GEMM; otherwise ``None``."""
+    name = getattr(first, "_bank_name", None)
+    if name is None or getattr(second, "_bank_name", None) != name or first.bias is not None or second.bias is not None:
+        return None
+    engine = getattr(getattr(first, "_bank_root", None), "_bank_engine", None)
+    if engine is None or second._bank_idx != first._bank_idx + 1 or not hasattr(engine, "linear_pair"):
+        return None
+    return lambda x: engine.linear_pair(x, name, first._bank_idx)
+
+
 class RMSNorm(nn.Module):
     def __init__(self, dim: int, eps: float):
         super().__init__()
@@ -59,8 +71,13 @@ class Attention(nn.Module):
         cfg = self.cfg
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         q = self.q_proj(x2d)
-        k = self.k_proj(x2d)
-        v = self.v_proj(x2d)
+        pair = _bank_pair(self.k_proj, self.v_proj)
+        if pair is not None:
+            kv = pair(x2d)                      # k and v are neighbouring bank slots: one GEMM, column-sliced
+            k, v = kv[:, : Hkv * D], kv[:, Hkv * D:]
+        else:
+            k = self.k_proj(x2d)
+            v = self.v_proj(x2d)
         qw = self.q_norm.weight if cfg.qk_norm else None
         kw = self.k_norm.weight if cfg.qk_norm else None
         q = ops.head_norm_rope(q, qw, cos_sin, Hq, S, D, cfg.rms_norm_eps)
@@ -77,6 +94,9 @@ class MLP(nn.Module):
         self.down_proj = Linear(cfg.intermediate_size, cfg.hidden_size, bias=False)
 
     def forward(self, x2d):
+        pair = _bank_pair(self.gate_proj, self.up_proj)
+        if pair is not None:
+            return self.down_proj(ops.swiglu_packed(pair(x2d)))
         return self.down_proj(ops.swiglu(self.gate_proj(x2d), self.up_proj(x2d)))
 
 

@@ -110,8 +110,8 @@ class _LinearFn(torch.autograd.Function):
     def backward(ctx, dy):
         x2, w = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
-        if not dy2.is_contiguous():
-            dy2 = dy2.contiguous()
+        if dy2.stride(-1) != 1 or dy2.stride(0) % 8 or dy2.data_ptr() % 16:
+            dy2 = dy2.contiguous()            # column slices of a wider buffer are consumed in place
         dx = gemm(dy2, w).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.sink is not None:
@@ -285,6 +285,39 @@ class _SwiGLUFn(torch.autograd.Function):
         _ext.ext().swiglu_bwd(dout, gate, up, dgate, dup)
         _count()
         return dgate, dup
+
+
+class _SwiGLUPackedFn(torch.autograd.Function):
+    """SwiGLU on a packed ``(tokens, 2*I)`` projection output ``[gate | up]``; the backward pass returns one
+    packed gradient, so the fused gate/up GEMM sees a single contiguous ``dy``."""
+
+    @staticmethod
+    def forward(ctx, gu):
+        I = gu.shape[1] // 2
+        out = torch.empty(gu.shape[0], I, device=gu.device, dtype=gu.dtype)
+        _ext.ext().swiglu_fwd(gu[:, :I], gu[:, I:], out)
+        _count()
+        ctx.save_for_backward(gu)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        I = gu.shape[1] // 2
+        if dout.stride(-1) != 1 or dout.stride(0) % 8:
+            dout = dout.contiguous()
+        dgu = torch.empty_like(gu)
+        _ext.ext().swiglu_bwd(dout, gu[:, :I], gu[:, I:], dgu[:, :I], dgu[:, I:])
+        _count()
+        return dgu
+
+
+def swiglu_packed(gu):
+    """``silu(gu[:, :I]) * gu[:, I:]`` for a packed gate/up projection output."""
+    I = gu.shape[1] // 2
+    if use_kernels(gu) and gu.dim() == 2 and I % 8 == 0 and gu.is_contiguous():
+        return _SwiGLUPackedFn.apply(gu)
+    return ref.swiglu(gu[:, :I], gu[:, I:])
 
 
 def swiglu(gate, up):

@@ -35,7 +35,8 @@ from .symm import SymmetricHeap, _world
 
 
 class _BankState:
-    __slots__ = ("spec", "n_local", "shard", "shard_off", "grad_full", "grad_off", "gathered", "param", "sinks")
+    __slots__ = ("spec", "n_local", "shard", "shard_off", "grad_full", "grad_off", "gathered", "param", "sinks",
+                 "pair_sinks")
 
 
 class ShardedEngine:
@@ -113,6 +114,8 @@ class ShardedEngine:
             setattr(model, b.spec.name, param)
             st.param = param
             st.sinks = [ops.GradSink(st.grad_full[i]) for i in range(n_pad)]
+            # neighbouring slots (k|v, gate|up) viewed as one (2H, W) matrix for the fused pair GEMMs
+            st.pair_sinks = {i: ops.GradSink(st.grad_full[i:i + 2].view(2 * H, W)) for i in range(0, n_pad - 1, 2)}
             self.state[b.spec.name] = st
             b.parameter = None            # the un-sharded original is released
         del bank_full
@@ -143,6 +146,12 @@ class ShardedEngine:
         st = self.state[bank_name]
         y = ops.linear(x, st.gathered[idx], sink=st.sinks[idx])
         return y if bias is None else y + bias
+
+    def linear_pair(self, x, bank_name: str, idx: int):
+        """Slots ``idx`` and ``idx+1`` applied as one ``(2H, W)`` projection (one GEMM in each direction)."""
+        st = self.state[bank_name]
+        H, W = st.spec.matrix_shape
+        return ops.linear(x, st.gathered[idx:idx + 2].view(2 * H, W), sink=st.pair_sinks[idx])
 
     @contextmanager
     def no_sync(self):
@@ -184,6 +193,8 @@ class ShardedEngine:
             flat.zero_()
         for st in self.state.values():
             for s in st.sinks:
+                s.reset()
+            for s in st.pair_sinks.values():
                 s.reset()
             if self.materialize_grads and set_to_none and self.world > 1:
                 st.param.grad = None

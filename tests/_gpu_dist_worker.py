@@ -1,0 +1,163 @@
+"""Worker run as one process per GPU by tests/test_gpu_multi.py."""
+
+import argparse
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def _cfg():
+    from himuon_b200.models import DecoderConfig
+
+    return DecoderConfig(model_type="qwen3", vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=3,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=128, tie_word_embeddings=True,
+                         max_position_embeddings=512)
+
+
+def _batches(rank, steps, grad_acc, device):
+    g = torch.Generator().manual_seed(100 + rank)
+    out = []
+    for _ in range(steps):
+        step = []
+        for _ in range(grad_acc):
+            ids = torch.randint(0, 2048, (2, 128), generator=g).to(device)
+            step.append({"input_ids": ids, "labels": ids})
+        out.append(step)
+    return out
+
+
+def scenario_collectives(device):
+    from himuon_b200 import ops
+    from himuon_b200.parallel.symm import SymmetricHeap
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    heap = SymmetricHeap(64 << 20, device, timeout_s=20.0)
+    for dtype, n in ((torch.bfloat16, 16 * world * 4099), (torch.float32, 16 * world * 513)):
+        buf, off = heap.alloc((n,), dtype)
+        for it in range(3):
+            g = torch.Generator().manual_seed(it)
+            vals = [torch.randn(n, generator=torch.Generator().manual_seed(10 * it + r)) for r in range(world)]
+            buf.copy_(vals[rank].to(dtype))
+            heap.allreduce_(buf, off, 1.0 / world)
+            want = sum(v.to(dtype).float() for v in vals) / world
+            torch.cuda.synchronize()
+            assert torch.allclose(buf.float().cpu(), want, atol=2e-2, rtol=2e-2), (dtype, it)
+    # peer views + barrier: every rank writes its id into the next rank's buffer
+    slot, off = heap.alloc((8,), torch.float32)
+    heap.barrier()
+    heap.view((rank + 1) % world, off, (8,), torch.float32).fill_(float(rank))
+    heap.barrier()
+    torch.cuda.synchronize()
+    assert slot[0].item() == float((rank - 1) % world)
+    ops.check_status()
+    dist.barrier()
+    if rank == 0:
+        print("COLLECTIVES OK", flush=True)
+    heap.close()
+
+
+def scenario_train(mode, optimizer_name, device):
+    from himuon_b200 import ops
+    from himuon_b200.models import CausalLM
+    from himuon_b200.optim import get_optimizer
+    from himuon_b200.trainer import Trainer
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.manual_seed(0)
+    model = CausalLM(_cfg()).to(device, torch.bfloat16)
+    if mode == "fsdp":
+        from himuon_b200.parallel.fsdp import ShardedEngine
+        engine = ShardedEngine(model, use_banks=True, timeout_s=30.0)
+    else:
+        from himuon_b200.parallel.ddp import DataParallelEngine
+        engine = DataParallelEngine(model, timeout_s=30.0)
+    lr = 1e-3 if optimizer_name == "adamw" else 0.02
+    ns = argparse.Namespace(lr=lr, weight_decay=0.1, tile_size=128, cuda_graph=True, cuda_graph_warmup=1)
+    opt = get_optimizer(optimizer_name, model, ns)
+    if mode == "fsdp":
+        engine.attach_optimizer(opt)
+    trainer = Trainer(model, opt, None, engine, grad_acc=2, device=device)
+    trainer.zero_set_to_none = False
+    steps = 4
+    losses = [float(trainer.train_step(b)) for b in _batches(rank, steps, 2, device)]
+    torch.cuda.synchronize()
+    ops.check_status()
+    all_losses = [None] * world
+    dist.all_gather_object(all_losses, losses)
+    sd = engine.full_state_dict() if mode == "fsdp" else {k: v.detach().cpu() for k, v in model.state_dict().items()}
+    if rank == 0:
+        torch.manual_seed(0)
+        ref_model = CausalLM(_cfg()).to(device, torch.bfloat16)
+        ns_ref = argparse.Namespace(lr=lr, weight_decay=0.1, tile_size=128, cuda_graph=False)
+        ref_opt = get_optimizer("muon" if optimizer_name == "muon-fsdp" else optimizer_name, ref_model, ns_ref)
+        per_rank = [_batches(r, steps, 2, device) for r in range(world)]
+        ref_losses = []
+        for s in range(steps):
+            tot = 0.0
+            for mb in range(2):
+                for r in range(world):
+                    b = per_rank[r][s][mb]
+                    loss = ref_model(b["input_ids"], labels=b["labels"]).loss
+                    (loss / (2 * world)).backward()
+                    tot += float(loss)
+            ref_opt.step()
+            ref_opt.zero_grad()
+            ref_losses.append(tot / (2 * world))
+        mean_losses = [sum(l[s] for l in all_losses) / world for s in range(steps)]
+        for a, b in zip(mean_losses, ref_losses):
+            assert abs(a - b) < 5e-2, (mean_losses, ref_losses)
+        assert mean_losses[-1] < mean_losses[0] + 0.05
+        ref_sd = ref_model.state_dict()
+        assert set(sd) == set(ref_sd), sorted(set(sd) ^ set(ref_sd))[:6]
+        cos = min(float(torch.nn.functional.cosine_similarity(sd[k].float().flatten().cpu(), ref_sd[k].float().flatten().cpu(), dim=0))
+                  for k in ref_sd)
+        assert cos > 0.999, cos
+        print(f"PARITY OK {mode} {optimizer_name} losses={mean_losses} ref={ref_losses} min_cos={cos:.6f}", flush=True)
+    dist.barrier()
+    engine.close()
+
+
+def scenario_timeout(device):
+    """One rank skips a barrier (host side only, nothing of it in flight): the other's bounded wait runs out,
+    the kernel returns, the status word reports it and the context stays usable."""
+    from himuon_b200 import ops
+    from himuon_b200.parallel.symm import SymmetricHeap
+
+    rank = dist.get_rank()
+    heap = SymmetricHeap(1 << 20, device, timeout_s=1.0)
+    if rank == 0:
+        heap.barrier()                       # nobody answers
+        torch.cuda.synchronize()
+        try:
+            ops.check_status()
+            print("UNEXPECTED: no timeout reported", flush=True)
+        except RuntimeError as e:
+            x = torch.ones(4, device=device) * 2          # the context still works
+            print(f"DETECTED {e} ; context alive {x.sum().item()}", flush=True)
+    dist.barrier()
+    heap.close()
+
+
+if __name__ == "__main__":
+    scenario, mode, optname = sys.argv[1], sys.argv[2], sys.argv[3]
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    device = torch.device(f"cuda:{local}")
+    dist.init_process_group("nccl", device_id=device)
+    try:
+        if scenario == "collectives":
+            scenario_collectives(device)
+        elif scenario == "train":
+            scenario_train(mode, optname, device)
+        else:
+            scenario_timeout(device)
+    except Exception:
+        import traceback
+        print("WORKER FAILED\n" + traceback.format_exc()[-1500:], flush=True)
+        raise
+    dist.barrier()
+    dist.destroy_process_group()

@@ -55,7 +55,7 @@ def _run(b_hw=None, cuda_graph=False, steps=5, dtype=torch.bfloat16):
     from himuon_b200.optimizers import HiMuon
 
     torch.manual_seed(0)
-    model = make_linear_model([(512, 768), (300, 520), (128, 128)], dtype, "cuda")
+    model = make_linear_model([(512, 768), (300, 520), (128, 128)], dtype).to("cuda")   # CPU init: same weights as the CPU run
     bias = torch.nn.Parameter(torch.zeros(64, device="cuda", dtype=dtype))
     opt = HiMuon([{"params": list(model.parameters())}, {"params": [bias], "use_muon": False, "lr": 1e-3}],
                  tile_size=128, b_hw=b_hw, cuda_graph=cuda_graph, cuda_graph_warmup=2)

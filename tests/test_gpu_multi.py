@@ -1,0 +1,42 @@
+"""Multi-GPU tier (needs >= 2 GPUs): the peer-memory collectives, data-parallel and bank-sharded training against a
+single-process run, and detection of a missing rank through a bounded device-side wait.  Each case runs as child
+processes, one per GPU, like the reference's tests/integration/test_himuon_fsdp_parity.py."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.distributed]
+HERE = os.path.dirname(os.path.abspath(__file__))
+N_GPUS = torch.cuda.device_count() if torch.cuda.is_available() else 0
+needs2 = pytest.mark.skipif(N_GPUS < 2, reason="needs at least 2 GPUs")
+
+
+def _run(nproc, *argv, timeout=600):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29700 + os.getpid() % 200),
+           os.path.join(HERE, "_gpu_dist_worker.py"), *argv]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+
+
+@needs2
+def test_peer_memory_collectives():
+    r = _run(min(N_GPUS, 8), "collectives", "-", "-")
+    assert "COLLECTIVES OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+@needs2
+@pytest.mark.parametrize("mode,opt", [("fsdp", "himuon"), ("ddp", "himuon"), ("fsdp", "muon-fsdp"), ("fsdp", "adamw")])
+def test_multi_gpu_training_matches_single_process(mode, opt):
+    r = _run(2, "train", mode, opt)
+    assert "PARITY OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+@needs2
+def test_missing_rank_surfaces_as_status_not_hang():
+    r = _run(2, "timeout", "-", "-", timeout=300)
+    assert "DETECTED" in r.stdout and "UNEXPECTED" not in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
