@@ -30,8 +30,31 @@ struct GemmDev {
   int round_acc;    // 1: round alpha*acc to bf16 before adding beta*aux
   int tiles_m, tiles_n, kblocks;
   int tma_store;    // 1: epilogue goes through shared-memory slabs and TMA stores (needs 16-byte aligned C rows)
+  // Work list: items [0, full_items) are whole tiles; each tile of the last, mostly empty wave is cut into
+  // `nslices` (2..4) K-ranges, one item each, whose fp32 partial sums meet in `ws`; the slice that arrives last
+  // adds the others to its accumulator and runs the epilogue.
+  int full_items, total_items, nslices, split_debug;
+  float* ws;        // [tail tile][slice][BM][BN] fp32
+  int* counters;    // arrivals per tail tile (self-resetting)
   int* status;
 };
+
+struct WorkItem { int tile, kb0, kb1, slice, tail; bool split; };
+__device__ __forceinline__ WorkItem decode_item(const GemmDev& p, int item) {
+  WorkItem w;
+  if (item < p.full_items) {
+    w.tile = item; w.kb0 = 0; w.kb1 = p.kblocks; w.slice = 0; w.tail = 0; w.split = false;
+  } else {
+    const int t = item - p.full_items;
+    w.tail = t / p.nslices;
+    w.slice = t - w.tail * p.nslices;
+    w.tile = p.full_items + w.tail;
+    w.kb0 = static_cast<int>(static_cast<long long>(p.kblocks) * w.slice / p.nslices);
+    w.kb1 = static_cast<int>(static_cast<long long>(p.kblocks) * (w.slice + 1) / p.nslices);
+    w.split = true;
+  }
+  return w;
+}
 
 constexpr int BM = 128;
 constexpr int BK = 64;
@@ -78,7 +101,8 @@ template <int BN, bool OUT_FP32>
 __device__ __forceinline__ void epilogue_tile_tma(const CUtensorMap* tmC, uint8_t* sC, uint32_t t_row, int row_in_tile,
                                                   int m0, int n0, int b, const void* aux, long long aux_row_off,
                                                   int M, int N, float alpha, float beta, int round_acc,
-                                                  uint32_t& slab_seq, bool issuer) {
+                                                  uint32_t& slab_seq, bool issuer, const float* partials = nullptr,
+                                                  int nslices = 1, int my_slice = 0) {
   constexpr int SW = OUT_FP32 ? 32 : 64;
   constexpr int SLABS = BN / SW;
   const bool row_ok = (m0 + row_in_tile) < M;
@@ -97,6 +121,25 @@ __device__ __forceinline__ void epilogue_tile_tma(const CUtensorMap* tmC, uint8_
       uint32_t v[32];
       tmem_ld32(t_row + sl * SW + ch * 32, v);
       tmem_ld_wait();
+      if (partials != nullptr) {
+        // split-K tail: add the other slices' partial sums (written by other CTAs, read past L1); all loads of a
+        // slice are issued before they are consumed
+        for (int q = 0; q < nslices; ++q) {
+          if (q == my_slice) continue;
+          const float4* src = reinterpret_cast<const float4*>(
+              partials + (static_cast<long long>(q) * BM + row_in_tile) * BN + sl * SW + ch * 32);
+          float4 t4[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) t4[j] = __ldcg(src + j);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v[4 * j + 0] = __float_as_uint(__uint_as_float(v[4 * j + 0]) + t4[j].x);
+            v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + t4[j].y);
+            v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + t4[j].z);
+            v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + t4[j].w);
+          }
+        }
+      }
       if (OUT_FP32) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -157,6 +200,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = abort_flag + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -180,7 +224,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
 
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
-  const int total_tiles = tiles_per_batch * p.batch;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -190,12 +233,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
+        const WorkItem w = decode_item(p, item);
+        const int tile = w.tile;
         const int b = tile / tiles_per_batch;
         const int r = tile - b * tiles_per_batch;
         const int mt = r % p.tiles_m;
         const int nt = r / p.tiles_m;
-        for (int kb = 0; kb < p.kblocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
           uint8_t* sA = smem + stage * STAGE_BYTES;
           uint8_t* sB = sA + A_BYTES;
@@ -227,11 +272,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
+        const WorkItem w = decode_item(p, item);
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag, p.status, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < p.kblocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 2)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_base = smem_u32(smem + stage * STAGE_BYTES);
@@ -242,7 +288,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                         : umma_smem_desc(a_base + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + k * 2048, CHUNK_BYTES, 1024)
                                         : umma_smem_desc(b_base + k * 32, 16, 1024);
-            umma_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -261,7 +307,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t slab_seq = 0;
     const bool issuer = (threadIdx.x == 128);
     if (issuer && p.tma_store) tma_prefetch_desc(&tmC);
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    for (int item = blockIdx.x; item < p.total_items; item += gridDim.x) {
+      const WorkItem w = decode_item(p, item);
+      const int tile = w.tile;
       const int b = tile / tiles_per_batch;
       const int r = tile - b * tiles_per_batch;
       const int mt = r % p.tiles_m;
@@ -272,12 +320,45 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int row_in_tile = ew * 32 + lane;
         const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(acc * BN);
         const long long aux_row = static_cast<long long>(b) * p.strideAux + static_cast<long long>(mt * BM + row_in_tile) * p.ldaux;
-        if (p.out_fp32)
-          epilogue_tile_tma<BN, true>(&tmC, sC, t_acc, row_in_tile, mt * BM, nt * BN, b, p.aux, aux_row, p.M, p.N,
-                                      p.alpha, p.beta, p.round_acc, slab_seq, issuer);
-        else
-          epilogue_tile_tma<BN, false>(&tmC, sC, t_acc, row_in_tile, mt * BM, nt * BN, b, p.aux, aux_row, p.M, p.N,
-                                       p.alpha, p.beta, p.round_acc, slab_seq, issuer);
+        const float* partials = nullptr;
+        bool run_epilogue = true;
+        if (w.split) {
+          // publish this slice's partial accumulator, then find out whether every other slice has arrived
+          float* tile_ws = p.ws + static_cast<long long>(w.tail) * p.nslices * BM * BN;
+          float* mine = tile_ws + (static_cast<long long>(w.slice) * BM + row_in_tile) * BN;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(t_acc + c0, v);
+            tmem_ld_wait();
+            if (p.split_debug & 1) continue;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              __stcg(reinterpret_cast<float4*>(mine + c0) + j,
+                     make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                 __uint_as_float(v[4 * j + 3])));
+          }
+          if (!(p.split_debug & 2)) __threadfence();
+          named_barrier(2, 128);
+          if (issuer) {
+            const int old = atomicAdd(p.counters + w.tail, 1);
+            const int last = (old == p.nslices - 1) ? 1 : 0;
+            if (last) p.counters[w.tail] = 0;          // ready for the next launch
+            *last_flag = last;
+          }
+          named_barrier(1, 128);
+          run_epilogue = (*last_flag != 0);
+          if (run_epilogue) { __threadfence(); partials = (p.split_debug & 4) ? nullptr : tile_ws; }
+          named_barrier(2, 128);                       // everyone has read last_flag before it can change again
+        }
+        if (run_epilogue) {
+          if (p.out_fp32)
+            epilogue_tile_tma<BN, true>(&tmC, sC, t_acc, row_in_tile, mt * BM, nt * BN, b, p.aux, aux_row, p.M, p.N,
+                                        p.alpha, p.beta, p.round_acc, slab_seq, issuer, partials, p.nslices, w.slice);
+          else
+            epilogue_tile_tma<BN, false>(&tmC, sC, t_acc, row_in_tile, mt * BM, nt * BN, b, p.aux, aux_row, p.M, p.N,
+                                         p.alpha, p.beta, p.round_acc, slab_seq, issuer, partials, p.nslices, w.slice);
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -391,18 +472,52 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
-// Developer knobs read once from the environment: HIMUON_GEMM_EPILOGUE=direct, HIMUON_GEMM_BN=128|192|256.
-struct GemmTuning { bool force_direct = false; int force_bn = 0; };
+// Developer knobs read once from the environment: HIMUON_GEMM_EPILOGUE=direct, HIMUON_GEMM_BN=128|192|256,
+// HIMUON_GEMM_SPLITK=1 (split the last wave along K; correct but off by default: the single reducing CTA reads the
+// other slices' partial tiles with too little memory parallelism, which costs more than the idle SMs it saves).
+struct GemmTuning { bool force_direct = false; bool no_split = true; int force_bn = 0; int split_debug = 0; int split_max = 4; };
 static const GemmTuning& tuning() {
   static GemmTuning t = [] {
     GemmTuning g;
     const char* e = getenv("HIMUON_GEMM_EPILOGUE");
     if (e && std::string(e) == "direct") g.force_direct = true;
+    const char* sp = getenv("HIMUON_GEMM_SPLITK");
+    if (sp) g.no_split = std::string(sp) != "1";
+    const char* sd = getenv("HIMUON_GEMM_SPLIT_DEBUG");
+    if (sd) g.split_debug = atoi(sd);
+    const char* sm = getenv("HIMUON_GEMM_SPLIT_MAX");
+    if (sm) g.split_max = atoi(sm);
     const char* b = getenv("HIMUON_GEMM_BN");
     if (b) g.force_bn = atoi(b);
     return g;
   }();
   return t;
+}
+
+// Scratch of the split-K tail: fp32 partial tiles and arrival counters, allocated once per device on first use
+// (well before any stream capture) and shared by every GEMM of the device, which therefore must not overlap each
+// other on different streams when they split.
+constexpr long long kSplitMaxItems = 160;  // slices of one launch (never more than the SM count)
+struct SplitWorkspace { float* ws = nullptr; int* counters = nullptr; };
+static SplitWorkspace& split_workspace() {
+  static SplitWorkspace per_device[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  SplitWorkspace& w = per_device[dev];
+  if (w.ws == nullptr) {
+    void* p1 = nullptr;
+    void* p2 = nullptr;
+    if (cudaMalloc(&p1, kSplitMaxItems * BM * 256 * sizeof(float)) == cudaSuccess &&
+        cudaMemset(p1, 0, kSplitMaxItems * BM * 256 * sizeof(float)) == cudaSuccess &&
+        cudaMalloc(&p2, kSplitMaxItems * sizeof(int)) == cudaSuccess && cudaMemset(p2, 0, kSplitMaxItems * sizeof(int)) == cudaSuccess) {
+      w.ws = static_cast<float*>(p1);
+      w.counters = static_cast<int*>(p2);
+    } else {
+      cudaGetLastError();   // splitting stays off on this device
+    }
+  }
+  return w;
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
@@ -457,7 +572,27 @@ static void launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   }
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batch;
   int sms = a.max_ctas > 0 ? a.max_ctas : num_sms();
-  const int grid = static_cast<int>(total < sms ? total : sms);
+  // Split-K for the last wave when it would leave more than half of the SMs idle.
+  p.full_items = static_cast<int>(total);
+  p.nslices = 1;
+  p.split_debug = tuning().split_debug;
+  p.ws = nullptr;
+  p.counters = nullptr;
+  const int rem = static_cast<int>(total % sms);
+  if (p.tma_store && !tuning().no_split && rem > 0 && rem * 2 <= sms && p.kblocks >= 16) {
+    int sl = sms / rem;
+    if (sl > p.kblocks / 8) sl = p.kblocks / 8;
+    if (sl > tuning().split_max) sl = tuning().split_max;   // the last slice reads (sl - 1) x 128 KB of partials
+    SplitWorkspace& wsp = split_workspace();
+    if (sl >= 2 && wsp.ws != nullptr && static_cast<long long>(rem) * sl <= kSplitMaxItems) {
+      p.nslices = sl;
+      p.full_items = static_cast<int>(total) - rem;
+      p.ws = wsp.ws;
+      p.counters = wsp.counters;
+    }
+  }
+  p.total_items = p.full_items + (p.nslices > 1 ? rem * p.nslices : 0);
+  const int grid = static_cast<int>(p.total_items < sms ? p.total_items : sms);
   kern<<<grid, 256, SMEM, stream>>>(tmA, tmB, tmC, p);
 }
 
