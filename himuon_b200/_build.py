@@ -14,6 +14,7 @@ EXT_NAME = "himuon_b200_C"
 
 CUDA_SOURCES = [
     "gemm_sm100.cu",
+    "gemm2_sm100.cu",
     "optim_kernels.cu",
     "model_kernels.cu",
     "attention_sm100.cu",

@@ -1,0 +1,171 @@
+// Pieces shared by the one-CTA and the CTA-pair GEMM kernels: launch parameters, the work-item decoder and the
+// TMA-store epilogue (TMEM -> registers -> fused epilogue -> swizzled shared-memory slab -> bulk tensor store).
+#pragma once
+
+#include "himuon.h"
+#include "sm100_common.cuh"
+
+namespace himuon {
+
+struct GemmDev {
+  void* C;
+  const void* aux;
+  int M, N, K, batch;
+  long long ldc, ldaux, strideC, strideAux;
+  float alpha, beta;
+  int out_fp32;     // 1: C/aux are fp32, 0: bf16
+  int round_acc;    // 1: round alpha*acc to bf16 before adding beta*aux
+  int tiles_m, tiles_n, kblocks;
+  int tma_store;    // 1: epilogue goes through shared-memory slabs and TMA stores (needs 16-byte aligned C rows)
+  // Work list: items [0, full_items) are whole tiles; each tile of the last, mostly empty wave is cut into
+  // `nslices` (2..4) K-ranges, one item each, whose fp32 partial sums meet in `ws`; the slice that arrives last
+  // adds the others to its accumulator and runs the epilogue.
+  int full_items, total_items, nslices, split_debug;
+  float* ws;        // [tail tile][slice][BM][BN] fp32
+  int* counters;    // arrivals per tail tile (self-resetting)
+  int* status;
+};
+
+struct WorkItem { int tile, kb0, kb1, slice, tail; bool split; };
+__device__ __forceinline__ WorkItem decode_item(const GemmDev& p, int item) {
+  WorkItem w;
+  if (item < p.full_items) {
+    w.tile = item; w.kb0 = 0; w.kb1 = p.kblocks; w.slice = 0; w.tail = 0; w.split = false;
+  } else {
+    const int t = item - p.full_items;
+    w.tail = t / p.nslices;
+    w.slice = t - w.tail * p.nslices;
+    w.tile = p.full_items + w.tail;
+    w.kb0 = static_cast<int>(static_cast<long long>(p.kblocks) * w.slice / p.nslices);
+    w.kb1 = static_cast<int>(static_cast<long long>(p.kblocks) * (w.slice + 1) / p.nslices);
+    w.split = true;
+  }
+  return w;
+}
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr uint32_t SLAB_BYTES = BM * 128;   // one staging slab: 128 rows x 128 bytes (64 bf16 or 32 fp32 columns)
+
+// Loads the 128 bytes of `aux` that belong to this thread's row of a slab (zeros when there is no aux).
+template <bool OUT_FP32>
+__device__ __forceinline__ void load_aux_slab(const void* aux, long long elem_off, bool row_ok, int valid_cols,
+                                              uint4 (&x)[8]) {
+  constexpr int SW = OUT_FP32 ? 32 : 64;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) x[j] = make_uint4(0, 0, 0, 0);
+  if (aux == nullptr || !row_ok || valid_cols <= 0) return;
+  if (OUT_FP32) {
+    const float* ptr = reinterpret_cast<const float*>(aux) + elem_off;
+    if (valid_cols >= SW && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = reinterpret_cast<const uint4*>(ptr)[j];
+    } else {
+      uint32_t* w = reinterpret_cast<uint32_t*>(x);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (j < valid_cols) w[j] = __float_as_uint(ptr[j]);
+    }
+  } else {
+    const __nv_bfloat16* ptr = reinterpret_cast<const __nv_bfloat16*>(aux) + elem_off;
+    if (valid_cols >= SW && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = reinterpret_cast<const uint4*>(ptr)[j];
+    } else {
+      uint32_t* w = reinterpret_cast<uint32_t*>(x);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float lo = (2 * j < valid_cols) ? __bfloat162float(ptr[2 * j]) : 0.f;
+        const float hi = (2 * j + 1 < valid_cols) ? __bfloat162float(ptr[2 * j + 1]) : 0.f;
+        w[j] = pack_bf16x2(lo, hi);
+      }
+    }
+  }
+}
+
+// Epilogue of one accumulator tile through swizzled shared-memory slabs and TMA stores.  Called by the 128
+// epilogue threads together.  `slab_seq` numbers the slabs this CTA has stored so far (selects the staging buffer).
+template <int BN, bool OUT_FP32>
+__device__ __forceinline__ void epilogue_tile_tma(const CUtensorMap* tmC, uint8_t* sC, uint32_t t_row, int row_in_tile,
+                                                  int m0, int n0, int b, const void* aux, long long aux_row_off,
+                                                  int M, int N, float alpha, float beta, int round_acc,
+                                                  uint32_t& slab_seq, bool issuer, const float* partials = nullptr,
+                                                  int nslices = 1, int my_slice = 0) {
+  constexpr int SW = OUT_FP32 ? 32 : 64;
+  constexpr int SLABS = BN / SW;
+  const bool row_ok = (m0 + row_in_tile) < M;
+  uint4 xa[8], xn[8];
+  load_aux_slab<OUT_FP32>(aux, aux_row_off + n0, row_ok, N - n0, xa);
+#pragma unroll 1
+  for (int sl = 0; sl < SLABS; ++sl) {
+    const int col = n0 + sl * SW;
+    if (col >= N) break;                                   // uniform over the 128 threads
+    if (sl + 1 < SLABS) load_aux_slab<OUT_FP32>(aux, aux_row_off + col + SW, row_ok, N - col - SW, xn);
+    named_barrier(1, 128);                                 // the staging buffer is free (issuer waited on its reads)
+    uint8_t* buf = sC + (slab_seq & 1) * SLAB_BYTES;
+    uint8_t* my_row = buf + row_in_tile * 128;
+#pragma unroll
+    for (int ch = 0; ch < SW / 32; ++ch) {
+      uint32_t v[32];
+      tmem_ld32(t_row + sl * SW + ch * 32, v);
+      tmem_ld_wait();
+      if (partials != nullptr) {
+        // split-K tail: add the other slices' partial sums (written by other CTAs, read past L1); all loads of a
+        // slice are issued before they are consumed
+        for (int q = 0; q < nslices; ++q) {
+          if (q == my_slice) continue;
+          const float4* src = reinterpret_cast<const float4*>(
+              partials + (static_cast<long long>(q) * BM + row_in_tile) * BN + sl * SW + ch * 32);
+          float4 t4[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) t4[j] = __ldcg(src + j);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v[4 * j + 0] = __float_as_uint(__uint_as_float(v[4 * j + 0]) + t4[j].x);
+            v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + t4[j].y);
+            v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + t4[j].z);
+            v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + t4[j].w);
+          }
+        }
+      }
+      if (OUT_FP32) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 o;
+          o.x = alpha * __uint_as_float(v[4 * j + 0]) + beta * __uint_as_float(xa[j].x);
+          o.y = alpha * __uint_as_float(v[4 * j + 1]) + beta * __uint_as_float(xa[j].y);
+          o.z = alpha * __uint_as_float(v[4 * j + 2]) + beta * __uint_as_float(xa[j].z);
+          o.w = alpha * __uint_as_float(v[4 * j + 3]) + beta * __uint_as_float(xa[j].w);
+          *reinterpret_cast<float4*>(my_row + ((j ^ (row_in_tile & 7)) << 4)) = o;
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 e = xa[ch * 4 + q];
+          const uint32_t ew[4] = {e.x, e.y, e.z, e.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            float f0 = alpha * __uint_as_float(v[8 * q + 2 * t]);
+            float f1 = alpha * __uint_as_float(v[8 * q + 2 * t + 1]);
+            if (round_acc) { f0 = round_bf16(f0); f1 = round_bf16(f1); }
+            o[t] = pack_bf16x2(f0 + beta * bf16_lo(ew[t]), f1 + beta * bf16_hi(ew[t]));
+          }
+          const int j = ch * 4 + q;
+          *reinterpret_cast<uint4*>(my_row + ((j ^ (row_in_tile & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    named_barrier(2, 128);                                 // the slab is complete
+    if (issuer) {
+      tma_store_3d(tmC, buf, col, m0, b);
+      tma_store_commit();
+      tma_store_wait_read<1>();                            // the other buffer's previous store has drained
+    }
+    ++slab_seq;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) xa[j] = xn[j];
+  }
+}
+
+}  // namespace himuon

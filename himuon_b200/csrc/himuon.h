@@ -36,6 +36,10 @@ struct GemmArgs {
   int max_ctas = 0;   // 0 = one CTA per SM
 };
 void gemm_bf16(const GemmArgs& args, cudaStream_t stream);
+// CTA-pair (cta_group::2) variant for 256 x 256 tiles; gemm_bf16 dispatches to it when gemm2_supported().
+bool gemm2_supported(const GemmArgs& args);
+void gemm2_bf16(const GemmArgs& args, cudaStream_t stream);
+
 
 // ---------------------------------------------------------------- optimizer kernels
 constexpr int kMaxSrc = 8;

@@ -35,7 +35,8 @@ def _close(out, ref, atol, rtol):
 
 
 @pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, False), (True, True)])
-@pytest.mark.parametrize("shape", [(256, 512, 384), (128, 128, 64), (200, 328, 136), (1024, 2560, 1024)])
+@pytest.mark.parametrize("shape", [(256, 512, 384), (128, 128, 64), (200, 328, 136), (1024, 2560, 1024), (520, 776, 2304),
+                                   (2048, 2560, 4096)])
 def test_gemm_majors(trans_a, trans_b, shape):
     M, N, K = shape
     torch.manual_seed(0)
