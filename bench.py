@@ -49,6 +49,9 @@ def parse():
     p.add_argument("--grad-acc", type=int, default=GRAD_ACC)
     p.add_argument("--tile", type=int, default=TILE)
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--engine", type=str, default="fsdp", choices=["fsdp", "ddp"],
+                   help="fsdp: bank-sharded engine (headline); ddp: replicated parameters + fused all-reduce")
+    p.add_argument("--optimizer", type=str, default="himuon", help="himuon | muon-fsdp | muon | adamw (headline: himuon)")
     return p.parse_args()
 
 
@@ -123,10 +126,16 @@ def run_ours(args):
     cfg = get_config(args.model)
     with torch.device(device):
         model = CausalLM(cfg).to(torch.bfloat16)
-    engine = ShardedEngine(model, use_banks=True)
-    ns = argparse.Namespace(lr=LR, weight_decay=WD, tile_size=args.tile, cuda_graph=True, cuda_graph_warmup=1)
-    optimizer = get_optimizer("himuon", model, ns)
-    engine.attach_optimizer(optimizer)
+    if args.engine == "fsdp":
+        engine = ShardedEngine(model, use_banks=args.optimizer in ("himuon", "muon-fsdp"))
+    else:
+        from himuon_b200.parallel.ddp import DataParallelEngine
+        engine = DataParallelEngine(model)
+    ns = argparse.Namespace(lr=LR if args.optimizer != "adamw" else 1e-3, weight_decay=WD, tile_size=args.tile, cuda_graph=True,
+                            cuda_graph_warmup=1)
+    optimizer = get_optimizer(args.optimizer, model, ns)
+    if args.engine == "fsdp":
+        engine.attach_optimizer(optimizer)
     scheduler = wsd_schedule(optimizer, 100, 0, 400, 0.1)
     trainer = Trainer(model, optimizer, scheduler, engine, args.grad_acc, device)
     trainer.zero_set_to_none = False
@@ -187,7 +196,8 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model, "global_batch": args.micro_batch * args.grad_acc * world,
                        "seq_len": args.seq_len, "micro_batch_per_gpu": args.micro_batch, "grad_acc": args.grad_acc,
-                       "parallelism": f"fsdp-banks{world}", "optimizer": f"himuon tile {args.tile}, lr {LR}, wd {WD}, cuda graph",
+                       "parallelism": f"fsdp-banks{world}" if args.engine == "fsdp" else f"dp{world}",
+                       "optimizer": f"{args.optimizer} tile {args.tile}, lr {ns.lr}, wd {WD}, cuda graph",
                        "activation_checkpointing": False,
                        "l2": "no flush: each step streams >8 GB of weights and activations (L2 is 126 MB)"},
             "optimizer_step_ms": opt_ms,

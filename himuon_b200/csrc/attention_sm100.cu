@@ -47,6 +47,7 @@ struct AttnDev {
   const void* o_in; const void* d_o;
   void* dq; void* dk; void* dv;
   int B, S, Hq, Hkv, nblk;
+  int split_heads;      // dkv kernel: 1 = one CTA per (KV block, query head) writing per-head partials
   long long ld_o, ld_do, ld_dq, ld_dk, ld_dv;
   float scale_log2, scale;
   int* status;
@@ -447,8 +448,14 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb = blockIdx.x;
-  const int hk = blockIdx.y, b = blockIdx.z;
-  const int G = p.Hq / p.Hkv;
+  const int b = blockIdx.z;
+  // Grouped heads: either this CTA walks all G query heads of KV head blockIdx.y, or (split_heads) it handles the
+  // single query head blockIdx.y and its output is a per-head partial that a later pass sums over the group.
+  const int Gall = p.Hq / p.Hkv;
+  const int G = p.split_heads ? 1 : Gall;
+  const int hk = p.split_heads ? blockIdx.y / Gall : blockIdx.y;
+  const int h_first = p.split_heads ? blockIdx.y : hk * Gall;
+  const int out_head = p.split_heads ? blockIdx.y : hk;
   const int nq = p.nblk - kb;          // query blocks kb .. nblk-1
   const int iters = G * nq;
 
@@ -475,7 +482,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tma_load_4d(sV + HALF_BYTES, &tmV, &bars->a_full, 64, hk, kb * AT, b);
       for (int it = 0; it < iters; ++it) {
         const int g = it / nq, qi = kb + (it - g * nq);
-        const int h = hk * G + g;
+        const int h = h_first + g;
         if (!mbar_wait(&bars->b_empty, (it & 1) ^ 1, abort_flag, p.status, 4)) break;
         mbar_expect_tx(&bars->b_full, 2 * TILE_BYTES);
         tma_load_4d(sQ, &tmQ, &bars->b_full, 0, h, qi * AT, b);
@@ -518,7 +525,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     bool ok = true;
     for (int it = 0; it < iters; ++it) {
       const int g = it / nq, qi = kb + (it - g * nq);
-      const int h = hk * G + g;
+      const int h = h_first + g;
       const int q_idx = qi * AT + row;
       const bool row_ok = q_idx < p.S;
       float lse2 = 0.f, delta = 0.f;
@@ -562,8 +569,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_after();
       const int k_idx = kb * AT + row;   // accumulator rows are key positions
       const bool row_ok = k_idx < p.S;
-      __nv_bfloat16* dkp = reinterpret_cast<__nv_bfloat16*>(p.dk) + (static_cast<long long>(b) * p.S + k_idx) * p.ld_dk + hk * HD;
-      __nv_bfloat16* dvp = reinterpret_cast<__nv_bfloat16*>(p.dv) + (static_cast<long long>(b) * p.S + k_idx) * p.ld_dv + hk * HD;
+      __nv_bfloat16* dkp = reinterpret_cast<__nv_bfloat16*>(p.dk) + (static_cast<long long>(b) * p.S + k_idx) * p.ld_dk + out_head * HD;
+      __nv_bfloat16* dvp = reinterpret_cast<__nv_bfloat16*>(p.dv) + (static_cast<long long>(b) * p.S + k_idx) * p.ld_dv + out_head * HD;
 #pragma unroll 1
       for (int c = 0; c < 8; ++c) {
         uint32_t v[32];
@@ -645,7 +652,20 @@ void flash_attn_bwd(const AttnArgs& a, cudaStream_t s) {
   const CUtensorMap tq = head_tmap(a.q, a.B, a.S, a.Hq, a.ld_q), tk = head_tmap(a.k, a.B, a.S, a.Hkv, a.ld_k),
                     tv = head_tmap(a.v, a.B, a.S, a.Hkv, a.ld_v), tdo = head_tmap(a.d_o, a.B, a.S, a.Hq, a.ld_do);
   flash_bwd_dq_kernel<<<dim3(p.nblk, a.Hq, a.B), 192, SMEM_DQ, s>>>(tq, tk, tv, tdo, p);
-  flash_bwd_dkv_kernel<<<dim3(p.nblk, a.Hkv, a.B), 192, SMEM_DKV, s>>>(tq, tk, tv, tdo, p);
+  const int G = a.Hq / a.Hkv;
+  if (G > 1 && a.dk_part != nullptr && a.dv_part != nullptr) {
+    // one CTA per (KV block, query head): G times more CTAs, balanced across the SMs; the per-head partial
+    // gradients are then summed over each group
+    AttnDev ps = p;
+    ps.split_heads = 1;
+    ps.dk = a.dk_part; ps.dv = a.dv_part; ps.ld_dk = a.ld_part; ps.ld_dv = a.ld_part;
+    flash_bwd_dkv_kernel<<<dim3(p.nblk, a.Hq, a.B), 192, SMEM_DKV, s>>>(tq, tk, tv, tdo, ps);
+    const long long tokens = static_cast<long long>(a.B) * a.S;
+    group_sum_heads(a.dk_part, a.dk, tokens, a.Hkv, G, a.ld_part, a.ld_dk, s);
+    group_sum_heads(a.dv_part, a.dv, tokens, a.Hkv, G, a.ld_part, a.ld_dv, s);
+  } else {
+    flash_bwd_dkv_kernel<<<dim3(p.nblk, a.Hkv, a.B), 192, SMEM_DKV, s>>>(tq, tk, tv, tdo, p);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("himuon flash_attn_bwd launch failed: ") + cudaGetErrorString(e));
 }

@@ -198,7 +198,8 @@ static void flash_attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::T
 }
 static void flash_attn_bwd(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                            const at::Tensor& o, const at::Tensor& lse, at::Tensor& dq, at::Tensor& dk, at::Tensor& dv,
-                           at::Tensor& delta, int64_t B, int64_t S, int64_t Hq, int64_t Hkv, double scale) {
+                           at::Tensor& delta, const c10::optional<at::Tensor>& dkv_part, int64_t B, int64_t S, int64_t Hq,
+                           int64_t Hkv, double scale) {
   HM_CHECK(q.is_cuda() && is_bf16(q) && is_bf16(k) && is_bf16(v) && is_bf16(o) && is_bf16(d_o) && is_bf16(dq) && is_bf16(dk) && is_bf16(dv) && is_f32(lse) && is_f32(delta), "flash_attn_bwd: dtypes");
   HM_CHECK(q.stride(1) == 1 && k.stride(1) == 1 && v.stride(1) == 1 && o.stride(1) == 1 && d_o.stride(1) == 1 && dq.stride(1) == 1 && dk.stride(1) == 1 && dv.stride(1) == 1, "flash_attn_bwd: unit inner strides");
   HM_CHECK(q.size(0) == B * S && q.size(1) == Hq * 128 && k.size(1) == Hkv * 128 && delta.numel() >= B * Hq * S, "flash_attn_bwd: shapes");
@@ -209,6 +210,14 @@ static void flash_attn_bwd(const at::Tensor& d_o, const at::Tensor& q, const at:
   a.B = (int)B; a.S = (int)S; a.Hq = (int)Hq; a.Hkv = (int)Hkv;
   a.ld_q = q.stride(0); a.ld_k = k.stride(0); a.ld_v = v.stride(0); a.ld_o = o.stride(0); a.ld_do = d_o.stride(0);
   a.ld_dq = dq.stride(0); a.ld_dk = dk.stride(0); a.ld_dv = dv.stride(0);
+  if (dkv_part.has_value()) {
+    const at::Tensor& t = dkv_part.value();     // (2, B*S, Hq*128): per-query-head dK and dV
+    HM_CHECK(t.is_cuda() && is_bf16(t) && t.is_contiguous() && t.dim() == 3 && t.size(0) == 2 && t.size(1) == B * S && t.size(2) == Hq * 128,
+             "flash_attn_bwd: dkv_part must be a contiguous (2, B*S, Hq*128) bf16 tensor");
+    a.dk_part = t.data_ptr();
+    a.dv_part = static_cast<char*>(t.data_ptr()) + t.stride(0) * 2;
+    a.ld_part = t.stride(1);
+  }
   a.scale = (float)scale;
   himuon::flash_attn_bwd(a, cur_stream());
 }

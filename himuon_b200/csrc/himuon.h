@@ -119,6 +119,8 @@ void embedding_bwd(const long long* ids, const void* dout, void* dtable, long lo
 void cross_entropy_fwd_bwd(void* logits, const long long* labels, float* loss_sum, float* count, float* lse_out,
                            long long rows, int vocab, long long ld, float grad_scale, const float* scale_dev,
                            long long ignore_index, cudaStream_t s);
+void group_sum_heads(const void* in, void* out, long long tokens, int hkv, int G, long long ld_in, long long ld_out,
+                     cudaStream_t s);
 void cast_copy(const void* src, void* dst, long long n, int src_fp32, int dst_fp32, float scale, cudaStream_t s);
 void bf16_add_to_f32(const void* src_bf16, float* dst, long long n, cudaStream_t s);
 
@@ -128,6 +130,8 @@ void bf16_add_to_f32(const void* src_bf16, float* dst, long long n, cudaStream_t
 struct AttnArgs {
   const void* q; const void* k; const void* v; void* o; float* lse;
   const void* d_o; void* dq; void* dk; void* dv; float* delta;
+  void* dk_part; void* dv_part;       // optional (B*S, Hq*128) scratch: per-query-head dK/dV, summed over each group afterwards
+  long long ld_part;
   int B, S, Hq, Hkv;
   long long ld_q, ld_k, ld_v, ld_o, ld_do, ld_dq, ld_dk, ld_dv;
   float scale;

@@ -154,6 +154,88 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
+// Warp-per-row variant for hidden sizes up to 5120: a warp keeps its row of x in registers, reduces the dot product
+// with shuffles (no block-wide barrier per row) and accumulates its dw contribution in registers over all the rows
+// it processes (a lane always owns the same columns); dy is re-read for the second pass (it is still in L1).
+// Eight rows are in flight per block; the block flushes dw once through shared memory.
+template <int ITERS>      // ITERS * 32 lanes * 8 elements columns at most
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                        __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_accum, int rows, int cols) {
+  extern __shared__ float s_dw[];
+  const int nv = cols >> 3;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) s_dw[i] = 0.f;
+  __syncthreads();
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  float dwp[ITERS][8];
+#pragma unroll
+  for (int a = 0; a < ITERS; ++a)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) dwp[a][q] = 0.f;
+  for (int r = blockIdx.x * 8 + warp; r < rows; r += gridDim.x * 8) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long long>(r) * cols);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + static_cast<long long>(r) * cols);
+    uint4 xv[ITERS];
+#pragma unroll
+    for (int a = 0; a < ITERS; ++a) {
+      const int i = lane + a * 32;
+      if (i < nv) xv[a] = xr[i];
+    }
+    const float rs = rstd[r];
+    float dot = 0.f;
+#pragma unroll
+    for (int a = 0; a < ITERS; ++a) {
+      const int i = lane + a * 32;
+      if (i < nv) {
+        const uint4 wv = wr[i], gv = gr[i];
+        const uint32_t xu[4] = {xv[a].x, xv[a].y, xv[a].z, xv[a].w}, gu[4] = {gv.x, gv.y, gv.z, gv.w},
+                       wu[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float xh0 = bf16_lo(xu[q]) * rs, xh1 = bf16_hi(xu[q]) * rs;
+          const float g0 = bf16_lo(gu[q]), g1 = bf16_hi(gu[q]);
+          dot += g0 * bf16_lo(wu[q]) * xh0 + g1 * bf16_hi(wu[q]) * xh1;
+          dwp[a][2 * q] += g0 * xh0;
+          dwp[a][2 * q + 1] += g1 * xh1;
+        }
+      }
+    }
+    const float mean = warp_sum(dot) / cols;
+    uint4* dr = reinterpret_cast<uint4*>(dx + static_cast<long long>(r) * cols);
+#pragma unroll
+    for (int a = 0; a < ITERS; ++a) {
+      const int i = lane + a * 32;
+      if (i < nv) {
+        const uint4 wv = wr[i], gv = gr[i];
+        const uint32_t xu[4] = {xv[a].x, xv[a].y, xv[a].z, xv[a].w}, gu[4] = {gv.x, gv.y, gv.z, gv.w},
+                       wu[4] = {wv.x, wv.y, wv.z, wv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float xh0 = bf16_lo(xu[q]) * rs, xh1 = bf16_hi(xu[q]) * rs;
+          o[q] = pack_bf16x2(rs * (bf16_lo(gu[q]) * bf16_lo(wu[q]) - xh0 * mean),
+                             rs * (bf16_hi(gu[q]) * bf16_hi(wu[q]) - xh1 * mean));
+        }
+        dr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+  if (dw_accum) {
+#pragma unroll
+    for (int a = 0; a < ITERS; ++a) {
+      const int i = lane + a * 32;
+      if (i < nv) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) atomicAdd(&s_dw[i * 8 + q], dwp[a][q]);
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) atomicAdd(dw_accum + i, s_dw[i]);
+  }
+}
+
 void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s) {
   if (rows <= 0) return;
   if (cols % 8) throw std::runtime_error("himuon rmsnorm: hidden size must be a multiple of 8");
@@ -165,6 +247,19 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
                  int cols, cudaStream_t s) {
   if (rows <= 0) return;
   if (cols % 8 || cols > 8 * 256 * kNormColIters) throw std::runtime_error("himuon rmsnorm_bwd: unsupported hidden size");
+  if (cols <= 20 * 256) {
+    const int blocks_needed = (rows + 7) / 8;
+    const int grid = blocks_needed < num_sms() ? blocks_needed : num_sms();   // ~240 registers: one block per SM
+    const size_t smem = cols * sizeof(float);
+    auto dyp = reinterpret_cast<const __nv_bfloat16*>(dy);
+    auto xp = reinterpret_cast<const __nv_bfloat16*>(x);
+    auto wp = reinterpret_cast<const __nv_bfloat16*>(w);
+    auto dxp = reinterpret_cast<__nv_bfloat16*>(dx);
+    if (cols <= 10 * 256) rmsnorm_bwd_warp_kernel<10><<<grid, 256, smem, s>>>(dyp, xp, wp, rstd, dxp, dw_accum, rows, cols);
+    else if (cols <= 16 * 256) rmsnorm_bwd_warp_kernel<16><<<grid, 256, smem, s>>>(dyp, xp, wp, rstd, dxp, dw_accum, rows, cols);
+    else rmsnorm_bwd_warp_kernel<20><<<grid, 256, smem, s>>>(dyp, xp, wp, rstd, dxp, dw_accum, rows, cols);
+    return;
+  }
   const int grid = rows < num_sms() * 4 ? rows : num_sms() * 4;
   rmsnorm_bwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
                                           reinterpret_cast<const __nv_bfloat16*>(w), rstd, reinterpret_cast<__nv_bfloat16*>(dx),
@@ -503,6 +598,36 @@ void cross_entropy_fwd_bwd(void* logits, const long long* labels, float* loss_su
   const int grid = static_cast<int>(rows < cap ? rows : cap);
   cross_entropy_kernel<<<grid, 1024, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(logits), labels, loss_sum, count, lse_out, rows,
                                              vocab, ld, grad_scale, scale_dev, ignore_index);
+}
+
+// ------------------------------------------------------------------------------------------------ head-group sum
+// out[t, hk, :] = sum_g in[t, hk*G + g, :] for 128-wide heads (gradients of grouped K/V heads).
+__global__ void __launch_bounds__(256)
+group_sum_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long tokens, int hkv, int G,
+                 long long ld_in, long long ld_out) {
+  const long long total = tokens * hkv * 16;      // 16 vectors of 8 elements per head
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int vec = static_cast<int>(i & 15);
+    const long long th = i >> 4;
+    const int hk = static_cast<int>(th % hkv);
+    const long long t = th / hkv;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int g = 0; g < G; ++g) {
+      const uint4 v = *reinterpret_cast<const uint4*>(in + t * ld_in + (hk * G + g) * 128 + vec * 8);
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { acc[2 * q] += bf16_lo(u[q]); acc[2 * q + 1] += bf16_hi(u[q]); }
+    }
+    *reinterpret_cast<uint4*>(out + t * ld_out + hk * 128 + vec * 8) =
+        make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+void group_sum_heads(const void* in, void* out, long long tokens, int hkv, int G, long long ld_in, long long ld_out,
+                     cudaStream_t s) {
+  if (tokens <= 0) return;
+  group_sum_kernel<<<ew_grid(tokens * hkv * 16), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(in),
+                                                            reinterpret_cast<__nv_bfloat16*>(out), tokens, hkv, G, ld_in, ld_out);
 }
 
 // ------------------------------------------------------------------------------------------------ casts

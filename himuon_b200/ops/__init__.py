@@ -249,8 +249,9 @@ class _FlashAttnFn(torch.autograd.Function):
         dk = dqkv[:, Hq * 128: (Hq + Hkv) * 128]
         dv = dqkv[:, (Hq + Hkv) * 128:]
         delta = torch.empty(B * Hq * S, device=q.device, dtype=torch.float32)
-        _ext.ext().flash_attn_bwd(do, q, k, v, o, lse, dq, dk, dv, delta, B, S, Hq, Hkv, float(scale))
-        _count(2)
+        part = torch.empty(2, q.shape[0], Hq * 128, device=q.device, dtype=q.dtype) if Hq > Hkv else None
+        _ext.ext().flash_attn_bwd(do, q, k, v, o, lse, dq, dk, dv, delta, part, B, S, Hq, Hkv, float(scale))
+        _count(4 if part is not None else 2)
         return dq, dk, dv, None, None, None, None, None
 
 

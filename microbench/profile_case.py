@@ -68,7 +68,8 @@ def case_attn():
     fl = 4 * B * Hq * S * S * 128 / 2 / 1e9
     ms = _time(lambda: ext().flash_attn_fwd(q, k, v, o, lse, B, S, Hq, Hkv, sc))
     do, dq, dk, dv, delta = torch.randn_like(q), torch.empty_like(q), torch.empty_like(k), torch.empty_like(k), torch.empty_like(lse)
-    msb = _time(lambda: ext().flash_attn_bwd(do, q, k, v, o, lse, dq, dk, dv, delta, B, S, Hq, Hkv, sc))
+    part = torch.empty(2, B * S, Hq * 128, device="cuda", dtype=torch.bfloat16)
+    msb = _time(lambda: ext().flash_attn_bwd(do, q, k, v, o, lse, dq, dk, dv, delta, part, B, S, Hq, Hkv, sc))
     print(f"attention B{B} S{S} H{Hq}/{Hkv}: fwd {ms:.3f} ms {fl / ms:.0f} TFLOP/s, bwd {msb:.3f} ms {2.5 * fl / msb:.0f} TFLOP/s")
 
 
@@ -96,8 +97,32 @@ def case_optim():
           f"ns_normalize {ms3:.3f} ms {3 * gb / ms3 * 1e3:.0f} GB/s")
 
 
+def case_step():
+    """One full training step (forward, backward, HiMuon step) of a small Qwen3-style model: every kernel of the
+    library launches at least once."""
+    import argparse
+
+    from himuon_b200.models import CausalLM, DecoderConfig
+    from himuon_b200.optim import get_optimizer
+
+    torch.manual_seed(0)
+    cfg = DecoderConfig(model_type="qwen3", vocab_size=32768, hidden_size=1024, intermediate_size=3072, num_hidden_layers=2,
+                        num_attention_heads=8, num_key_value_heads=4, head_dim=128, tie_word_embeddings=True,
+                        max_position_embeddings=2048)
+    model = CausalLM(cfg).to("cuda", torch.bfloat16)
+    opt = get_optimizer("himuon", model, argparse.Namespace(lr=0.01, weight_decay=0.1, tile_size=512, cuda_graph=False))
+    ids = torch.randint(0, cfg.vocab_size, (4, 1024), device="cuda")
+    for _ in range(2):
+        loss = model(ids, labels=ids).loss
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=False)
+    torch.cuda.synchronize()
+    print(f"step case done, loss {loss.item():.3f}")
+
+
 CASES = {"gemm": case_gemm, "gemm_wgrad": case_gemm_wgrad, "ns512": case_ns512, "ns128": case_ns128, "attn": case_attn,
-         "optim": case_optim}
+         "optim": case_optim, "step": case_step}
 
 if __name__ == "__main__":
     for name in sys.argv[1:] or list(CASES):

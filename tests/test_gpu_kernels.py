@@ -339,7 +339,7 @@ def test_flash_attention_fwd_bwd(B, S, Hq, Hkv):
     ref.backward(do.float().view(B, S, Hq, D))
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     delta = torch.empty(B * Hq * S, device="cuda")
-    e.flash_attn_bwd(do, q, k, v, o, lse, dq, dk, dv, delta, B, S, Hq, Hkv, scale)
+    e.flash_attn_bwd(do, q, k, v, o, lse, dq, dk, dv, delta, torch.empty(2, B * S, Hq * 128, device='cuda', dtype=torch.bfloat16) if Hq > Hkv else None, B, S, Hq, Hkv, scale)
     torch.cuda.synchronize()
     _assert_status_clean()
     _close(dq, qr.grad.reshape(B * S, Hq * D), atol=3e-2, rtol=3e-2)
