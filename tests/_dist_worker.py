@@ -77,6 +77,38 @@ def scenario_train(mode, optimizer_name):
     engine.close()
 
 
+def scenario_dtensor():
+    """HiMuon on a DTensor bank sharded on the layer axis (what torch FSDP2 produces) against per-matrix HiMuon on one
+    process, with injected gradients: divisible and zero-padded tiles (reference: tests/integration/_fsdp_worker.py)."""
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+
+    from himuon_b200.optimizers import HiMuon
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    mesh = init_device_mesh("cpu", (world,))
+    for (H, W) in ((64, 96), (50, 75)):
+        torch.manual_seed(0)
+        full = torch.randn(8, H, W) * 0.02
+        bank = torch.nn.Parameter(distribute_tensor(full.clone(), mesh, [Shard(0)]))
+        opt = HiMuon([bank], tile_size=32, cuda_graph=False, lr=0.02)
+        mats = [torch.nn.Parameter(full[i].clone()) for i in range(8)]
+        ref_opt = HiMuon(mats, tile_size=32, cuda_graph=False, lr=0.02)
+        assert opt._has_dtensor_muon()
+        for s in range(4):
+            g = torch.randn(8, H, W, generator=torch.Generator().manual_seed(s))
+            bank.grad = distribute_tensor(g.clone(), mesh, [Shard(0)])
+            for i, m in enumerate(mats):
+                m.grad = g[i].clone()
+            opt.step()
+            ref_opt.step()
+        got = bank.detach().full_tensor()
+        want = torch.stack([m.detach() for m in mats])
+        assert torch.allclose(got, want, atol=1e-5, rtol=1e-4), (got - want).abs().max()
+    if rank == 0:
+        print("PARITY OK dtensor", flush=True)
+
+
 def scenario_missing_rank():
     """A rank that never joins: the others' collective ends with an error instead of hanging."""
     rank = dist.get_rank()
@@ -98,6 +130,8 @@ if __name__ == "__main__":
     dist.init_process_group("gloo", timeout=timeout)
     if scenario == "train":
         scenario_train(mode, optname)
+    elif scenario == "dtensor":
+        scenario_dtensor()
     else:
         scenario_missing_rank()
     if scenario != "missing":
