@@ -15,49 +15,11 @@
 //
 // The reference reaches attention through HF `sdpa` (PyTorch library kernels); it ships no
 // attention code of its own.
-#include "himuon.h"
-#include "sm100_common.cuh"
-#include "tma_host.h"
+#include "attention_common.cuh"
+
+#include <cstdlib>
 
 namespace himuon {
-
-constexpr int AT = 128;                 // tile rows (queries) and tile columns (keys)
-constexpr int HD = 128;                 // head dim
-constexpr uint32_t TILE_BYTES = AT * HD * 2;   // 32 KB: two 64-column halves of 16 KB
-constexpr uint32_t HALF_BYTES = 16384;
-constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
-
-// Byte offset of the 16-byte chunk `c16` (0..15) of row `r` in a [128 rows][128 cols] bf16 tile
-// stored as two K-major SWIZZLE_128B halves.
-__device__ __forceinline__ uint32_t sw128_off(int r, int c16) {
-  return static_cast<uint32_t>((c16 >> 3) * HALF_BYTES + r * 128 + (((c16 & 7) ^ (r & 7)) << 4));
-}
-// K-major operand descriptor for k-step ks (16 columns each) of such a tile.
-__device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int ks) {
-  return umma_smem_desc(base + (ks >> 2) * HALF_BYTES + (ks & 3) * 32, 16, 1024);
-}
-// MN-major operand descriptor for k-step ks (16 rows each) of the same bytes viewed as [K rows][M/N cols].
-__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int ks) {
-  return umma_smem_desc(base + ks * 2048, HALF_BYTES, 1024);
-}
-
-struct AttnDev {
-  void* o; float* lse; float* delta;
-  const void* o_in; const void* d_o;
-  void* dq; void* dk; void* dv;
-  int B, S, Hq, Hkv, nblk;
-  int split_heads;      // dkv kernel: 1 = one CTA per (KV block, query head) writing per-head partials
-  long long ld_o, ld_do, ld_dq, ld_dk, ld_dv;
-  float scale_log2, scale;
-  int* status;
-};
-
-struct AttnBars {
-  uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_empty[2], p_ready, o_done;
-  uint32_t tmem_slot;
-  int abort_flag;
-};
 
 // ================================================================================================ forward
 __global__ void __launch_bounds__(192, 1)
@@ -267,12 +229,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }
 
 // ================================================================================================ backward: dQ
-struct BwdBars {
-  uint64_t a_full, a_empty, b_full, b_empty, sp_full, ds_ready, acc_done;
-  uint32_t tmem_slot;
-  int abort_flag;
-};
-
 // CTA = (query block, head, batch).  Resident: Q, dO.  Streamed: K_j, V_j.  TMEM: S | dP | dQ.
 __global__ void __launch_bounds__(192, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -600,21 +556,29 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 }
 
 // ================================================================================================ host
-static CUtensorMap head_tmap(const void* ptr, int B, int S, int H, long long ld) {
-  // dims (innermost first): head_dim, heads, sequence, batch
-  const uint64_t dims[4] = {HD, static_cast<uint64_t>(H), static_cast<uint64_t>(S), static_cast<uint64_t>(B)};
-  const uint64_t strides[3] = {HD * 2, static_cast<uint64_t>(ld) * 2, static_cast<uint64_t>(ld) * 2 * static_cast<uint64_t>(S)};
-  const uint32_t box[4] = {64, 1, AT, 1};
-  return make_tmap(ptr, 4, dims, strides, box, 2, true);
-}
-
 static void check_attn(const AttnArgs& a) {
   if (a.S <= 0 || a.B <= 0 || a.Hq <= 0 || a.Hkv <= 0 || a.Hq % a.Hkv) throw std::runtime_error("himuon attention: bad sizes");
   if (a.ld_q % 8 || a.ld_k % 8 || a.ld_v % 8 || a.ld_o % 8) throw std::runtime_error("himuon attention: token strides must be multiples of 8");
 }
 
+// HIMUON_ATTN_KV=128 selects the one-CTA-per-SM kernels with 128-wide KV blocks for the forward and dQ passes
+// (default: the 64-wide, two-CTAs-per-SM kernels of attention_kv64_sm100.cu).
+static bool use_kv64() {
+  static const bool v = [] {
+    const char* e = getenv("HIMUON_ATTN_KV");
+    return !(e && std::string(e) == "128");
+  }();
+  return v;
+}
+
 void flash_attn_fwd(const AttnArgs& a, cudaStream_t s) {
   check_attn(a);
+  if (use_kv64()) {
+    flash_fwd_kv64(a, s);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) throw std::runtime_error(std::string("himuon flash_attn_fwd launch failed: ") + cudaGetErrorString(e));
+    return;
+  }
   constexpr size_t SMEM = 1024 + 6 * TILE_BYTES + 512;
   static bool attr = false;
   if (!attr) { cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM); attr = true; }
@@ -651,7 +615,8 @@ void flash_attn_bwd(const AttnArgs& a, cudaStream_t s) {
   p.status = status_word_ptr();
   const CUtensorMap tq = head_tmap(a.q, a.B, a.S, a.Hq, a.ld_q), tk = head_tmap(a.k, a.B, a.S, a.Hkv, a.ld_k),
                     tv = head_tmap(a.v, a.B, a.S, a.Hkv, a.ld_v), tdo = head_tmap(a.d_o, a.B, a.S, a.Hq, a.ld_do);
-  flash_bwd_dq_kernel<<<dim3(p.nblk, a.Hq, a.B), 192, SMEM_DQ, s>>>(tq, tk, tv, tdo, p);
+  if (use_kv64()) flash_bwd_dq_kv64(a, s);
+  else flash_bwd_dq_kernel<<<dim3(p.nblk, a.Hq, a.B), 192, SMEM_DQ, s>>>(tq, tk, tv, tdo, p);
   const int G = a.Hq / a.Hkv;
   if (G > 1 && a.dk_part != nullptr && a.dv_part != nullptr) {
     // one CTA per (KV block, query head): G times more CTAs, balanced across the SMs; the per-head partial
