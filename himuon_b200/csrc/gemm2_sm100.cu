@@ -16,6 +16,8 @@
 #include "sm100_common.cuh"
 #include "tma_host.h"
 
+#include <cstdlib>
+
 namespace himuon {
 
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;   // clears the CTA-rank bit of a shared::cluster address (pair leader)
@@ -71,7 +73,7 @@ constexpr int BNH = 128;     // rows of B staged by each CTA
 template <int STAGES, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ CUtensorMap tmC, GemmDev p) {
+                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmW, GemmDev p) {
   constexpr uint32_t A_BYTES = BM * BK * 2;
   constexpr uint32_t B_BYTES = BNH * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -113,7 +115,6 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
-  const int total_tiles = tiles_per_batch * p.batch;
   const int pair = blockIdx.x >> 1;
   const int n_pairs = gridDim.x >> 1;
 
@@ -125,14 +126,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < total_tiles; tile += n_pairs) {
+      for (int item = pair; ok && item < p.total_items; item += n_pairs) {
+        const WorkItem w = decode_item(p, item);
+        const int tile = w.tile;
         const int b = tile / tiles_per_batch;
         const int r = tile - b * tiles_per_batch;
         const int mt = r % p.tiles_m;
         const int nt = r / p.tiles_m;
         const int m0 = mt * 2 * BM + static_cast<int>(rank) * BM;
         const int n0 = nt * BN2 + static_cast<int>(rank) * BNH;
-        for (int kb = 0; kb < p.kblocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
           uint8_t* sA = smem + stage * STAGE_BYTES;
           uint8_t* sB = sA + A_BYTES;
@@ -162,11 +165,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < total_tiles; tile += n_pairs) {
+      for (int item = pair; ok && item < p.total_items; item += n_pairs) {
+        const WorkItem w = decode_item(p, item);
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag, p.status, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN2);
-        for (int kb = 0; kb < p.kblocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, p.status, 2)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_base = smem_u32(smem + stage * STAGE_BYTES);
@@ -177,7 +181,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                                         : umma_smem_desc(a_base + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + k * 2048, CHUNK_BYTES, 1024)
                                         : umma_smem_desc(b_base + k * 32, 16, 1024);
-            umma2_ss(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma2_ss(d_tmem, adesc, bdesc, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           }
           const uint32_t e_addr = smem_u32(&empty[stage]);
           umma2_commit(e_addr);                    // this CTA's producer
@@ -200,7 +204,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint32_t slab_seq = 0;
     const bool issuer = (threadIdx.x == 128);
     if (issuer) tma_prefetch_desc(&tmC);
-    for (int tile = pair; tile < total_tiles; tile += n_pairs) {
+    for (int item = pair; item < p.total_items; item += n_pairs) {
+      const WorkItem w = decode_item(p, item);
+      const int tile = w.tile;
       const int b = tile / tiles_per_batch;
       const int r = tile - b * tiles_per_batch;
       const int mt = r % p.tiles_m;
@@ -211,7 +217,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int m0 = mt * 2 * BM + static_cast<int>(rank) * BM;
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(acc * BN2);
       const long long aux_row = static_cast<long long>(b) * p.strideAux + static_cast<long long>(m0 + row_in_tile) * p.ldaux;
-      if (m0 < p.M) {                     // uniform: the second CTA of a ragged last row block has nothing to store
+      if (w.split) {
+        // K-slice of a last-wave tile: add the fp32 partial into the scratch tile (rows tail*256 + rank*128 ..);
+        // a follow-up kernel applies the epilogue to the complete sums
+        epilogue_tile_tma<BN2, true>(&tmW, sC, t_acc, row_in_tile, w.tail * 2 * BM + static_cast<int>(rank) * BM, 0, 0, nullptr, 0,
+                                     1 << 30, BN2, 1.f, 0.f, 0, slab_seq, issuer, nullptr, 1, 0, true);
+      } else if (m0 < p.M) {              // uniform: the second CTA of a ragged last row block has nothing to store
         if (p.out_fp32)
           epilogue_tile_tma<BN2, true>(&tmC, sC, t_acc, row_in_tile, m0, nt * BN2, b, p.aux, aux_row, p.M, p.N, p.alpha,
                                        p.beta, p.round_acc, slab_seq, issuer);
@@ -225,7 +236,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-    if (issuer) tma_store_wait_read<0>();
+    if (issuer) tma_store_wait_all();      // reductions into the scratch tiles are complete before the kernel ends
   }
 
   tc_fence_before();
@@ -235,6 +246,73 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     tc_fence_after();
     tmem_dealloc2(tmem_base, 512);
   }
+}
+
+// Second half of the split-K tail: turns the complete fp32 sums of the last-wave tiles into outputs (alpha, beta*aux,
+// optional bf16 rounding point, cast) and leaves the scratch zeroed for the next launch.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gemm2_finish_kernel(float* __restrict__ ws, GemmDev p, int first_tail_tile, int n_tail) {
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const long long per_tile = 256LL * 256 / 4;            // float4 groups per tile
+  const long long total = per_tile * n_tail;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / per_tile);
+    const int e = static_cast<int>(i - t * per_tile);
+    const int r = e >> 6, c = (e & 63) * 4;
+    float4* src = reinterpret_cast<float4*>(ws + (static_cast<long long>(t) * 256 + r) * 256 + c);
+    const float4 v = *src;
+    *src = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int tile = first_tail_tile + t;
+    const int b = tile / tiles_per_batch;
+    const int rr = tile - b * tiles_per_batch;
+    const int row = (rr % p.tiles_m) * 256 + r;
+    const int col = (rr / p.tiles_m) * 256 + c;
+    if (row >= p.M) continue;
+    const float vals[4] = {v.x, v.y, v.z, v.w};
+    T* cp = reinterpret_cast<T*>(p.C) + static_cast<long long>(b) * p.strideC + static_cast<long long>(row) * p.ldc + col;
+    const T* xp = p.aux ? reinterpret_cast<const T*>(p.aux) + static_cast<long long>(b) * p.strideAux +
+                              static_cast<long long>(row) * p.ldaux + col
+                        : nullptr;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (col + j >= p.N) break;
+      float o = p.alpha * vals[j];
+      if (xp) {
+        if (p.round_acc) o = round_bf16(o);
+        if (sizeof(T) == 2) o += p.beta * __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(xp)[j]);
+        else o += p.beta * reinterpret_cast<const float*>(xp)[j];
+      }
+      if (sizeof(T) == 2) reinterpret_cast<__nv_bfloat16*>(cp)[j] = __float2bfloat16_rn(o);
+      else reinterpret_cast<float*>(cp)[j] = o;
+    }
+  }
+}
+
+// fp32 scratch for the split-K tail of the pair kernel: up to kPairTailMax tiles of 256 x 256, zero between launches.
+// One buffer per device, shared by every GEMM of that device (GEMMs that split must not overlap on different streams).
+constexpr int kPairTailMax = 40;
+static float* pair_scratch() {
+  static float* per_device[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (per_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    const size_t bytes = static_cast<size_t>(kPairTailMax) * 256 * 256 * sizeof(float);
+    if (cudaMalloc(&ptr, bytes) == cudaSuccess && cudaMemset(ptr, 0, bytes) == cudaSuccess) per_device[dev] = static_cast<float*>(ptr);
+    else cudaGetLastError();
+  }
+  return per_device[dev];
+}
+
+static bool pair_split_enabled() {
+  static const bool v = [] {
+    const char* e = getenv("HIMUON_GEMM_PAIR_SPLITK");
+    return !(e && std::string(e) == "0");
+  }();
+  return v;
 }
 
 template <int STAGES, bool A_MN, bool B_MN>
@@ -300,8 +378,34 @@ static void launch_gemm2(const GemmArgs& a, cudaStream_t stream) {
   }
   int cap = max_pairs;
   if (a.max_ctas > 0 && a.max_ctas / 2 < cap) cap = a.max_ctas / 2 > 0 ? a.max_ctas / 2 : 1;
-  const long long pairs = total < cap ? total : cap;
-  kern<<<static_cast<int>(2 * pairs), 256, SMEM, stream>>>(tmA, tmB, tmC, p);
+  // Split the tiles of a mostly idle last wave along K: each K-slice adds its fp32 partial tile into a scratch tile
+  // with TMA reductions and a small follow-up kernel applies the epilogue.
+  CUtensorMap tmW = tmC;
+  const int rem = static_cast<int>(total % cap);
+  float* scratch = nullptr;
+  if (pair_split_enabled() && total > cap / 2 && rem > 0 && rem * 2 <= cap && rem <= kPairTailMax && p.kblocks >= 16 &&
+      (scratch = pair_scratch()) != nullptr) {
+    int sl = cap / rem;
+    if (sl > p.kblocks / 8) sl = p.kblocks / 8;
+    // worth it only when the K-blocks saved outweigh the fp32 reduction traffic and the second launch (~12 us)
+    if (sl >= 2 && (sl - 1) * p.kblocks / sl >= 40) {
+      p.nslices = sl;
+      p.full_items = static_cast<int>(total) - rem;
+      p.total_items = p.full_items + rem * sl;
+      const uint64_t dimsW[3] = {256, static_cast<uint64_t>(kPairTailMax) * 256, 1};
+      const uint64_t strW[2] = {256 * sizeof(float), static_cast<uint64_t>(kPairTailMax) * 256 * 256 * sizeof(float)};
+      const uint32_t boxW[3] = {32, BM, 1};
+      tmW = make_tmap(scratch, 3, dimsW, strW, boxW, 4, true);
+    }
+  }
+  const long long pairs = p.total_items < cap ? p.total_items : cap;
+  kern<<<static_cast<int>(2 * pairs), 256, SMEM, stream>>>(tmA, tmB, tmC, tmW, p);
+  if (p.nslices > 1) {
+    const long long groups = 256LL * 256 / 4 * rem;
+    const int blocks = static_cast<int>((groups + 255) / 256 < num_sms() * 4 ? (groups + 255) / 256 : num_sms() * 4);
+    if (a.out_fp32) gemm2_finish_kernel<float><<<blocks, 256, 0, stream>>>(scratch, p, p.full_items, rem);
+    else gemm2_finish_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(scratch, p, p.full_items, rem);
+  }
 }
 
 // True when the pair kernel can run this problem and is expected to win: TMA-storable output, more than one CTA

@@ -21,7 +21,7 @@ struct GemmDev {
   // `nslices` (2..4) K-ranges, one item each, whose fp32 partial sums meet in `ws`; the slice that arrives last
   // adds the others to its accumulator and runs the epilogue.
   int full_items, total_items, nslices, split_debug;
-  float* ws;        // [tail tile][slice][BM][BN] fp32
+  float* ws;        // one-CTA kernel: [tail tile][slice][BM][BN] fp32; pair kernel: [tail tile][256][256] fp32 running sums
   int* counters;    // arrivals per tail tile (self-resetting)
   int* status;
 };
@@ -89,7 +89,7 @@ __device__ __forceinline__ void epilogue_tile_tma(const CUtensorMap* tmC, uint8_
                                                   int m0, int n0, int b, const void* aux, long long aux_row_off,
                                                   int M, int N, float alpha, float beta, int round_acc,
                                                   uint32_t& slab_seq, bool issuer, const float* partials = nullptr,
-                                                  int nslices = 1, int my_slice = 0) {
+                                                  int nslices = 1, int my_slice = 0, bool reduce_add = false) {
   constexpr int SW = OUT_FP32 ? 32 : 64;
   constexpr int SLABS = BN / SW;
   const bool row_ok = (m0 + row_in_tile) < M;
@@ -158,7 +158,8 @@ __device__ __forceinline__ void epilogue_tile_tma(const CUtensorMap* tmC, uint8_
     fence_proxy_async_smem();
     named_barrier(2, 128);                                 // the slab is complete
     if (issuer) {
-      tma_store_3d(tmC, buf, col, m0, b);
+      if (reduce_add) tma_reduce_add_3d(tmC, buf, col, m0, b);     // split-K: accumulate into the fp32 scratch tile
+      else tma_store_3d(tmC, buf, col, m0, b);
       tma_store_commit();
       tma_store_wait_read<1>();                            // the other buffer's previous store has drained
     }

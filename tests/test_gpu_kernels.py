@@ -69,6 +69,31 @@ def test_gemm_batched_epilogue_and_fp32_accumulate():
     _close(acc, ref2, atol=1e-2, rtol=1e-3)
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 2560, 2560), (2000, 2560, 9728), (2560, 2304, 2048)])
+def test_gemm_pair_split_tail(M, N, K):
+    """Shapes whose last wave of 256x256 tiles is mostly idle: the tail tiles are cut along K, summed in an fp32
+    scratch by TMA reductions and finished by a second kernel.  Run twice (the scratch must come back zeroed), with
+    the aux epilogue and with fp32 accumulation into the output."""
+    torch.manual_seed(2)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    aux = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    for _ in range(2):
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        _ext().gemm(a, b, out, None, False, True, 1.0, 0.0, False, 0)
+        _close(out, ref, atol=0.3, rtol=2e-2)
+        out2 = torch.empty_like(out)
+        _ext().gemm(a, b, out2, aux, False, True, 0.5, -1.5, False, 0)
+        _close(out2, 0.5 * ref - 1.5 * aux.float(), atol=0.3, rtol=2e-2)
+    acc = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    ref2 = acc + ref
+    _ext().gemm(a, b, acc, acc, False, True, 1.0, 1.0, False, 0)
+    torch.cuda.synchronize()
+    _assert_status_clean()
+    _close(acc, ref2, atol=2e-2, rtol=1e-3)
+
+
 def _ns_ref(x, steps=5):
     a, b, c = 3.4445, -4.7750, 2.0315
     X = x.float()
