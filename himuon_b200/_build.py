@@ -18,7 +18,7 @@ CUDA_SOURCES = [
     "optim_kernels.cu",
     "model_kernels.cu",
     "attention_sm100.cu",
-    "attention_kv64_sm100.cu",
+    "attention_kv64_sm100.cu", "attention_bwd_sm100.cu",
     "ns5_sm100.cu",
     "comm_kernels.cu",
     "rmsnorm_bwd_noalloc.cu",

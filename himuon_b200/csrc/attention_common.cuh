@@ -61,8 +61,24 @@ inline CUtensorMap head_tmap(const void* ptr, int B, int S, int H, long long ld,
 }
 
 
+// CTAs start in linear block order (x fastest).  The causal work of a CTA depends only on its position along the
+// sequence, so that position is decoded as the slowest coordinate: all the heaviest blocks start first and the
+// light ones fill the tail of the launch (longest-processing-time order).  `sblk` counts from 0 = first started.
+__device__ __forceinline__ void attn_block_coords(int& sblk, int& head, int& batch) {
+  const int lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  const int per = gridDim.y * gridDim.z;
+  sblk = lin / per;
+  const int r = lin - sblk * per;
+  batch = r / gridDim.y;
+  head = r - batch * gridDim.y;
+}
+
 // 64-wide KV-block kernels (two CTAs per SM): forward and dQ.
 void flash_fwd_kv64(const AttnArgs& a, cudaStream_t s);
 void flash_bwd_dq_kv64(const AttnArgs& a, cudaStream_t s);
+
+// dK/dV pass in the transposed formulation (P^T and dS^T stay in tensor memory); S must be a multiple of 128.
+bool flash_bwd_dkv_t_supported(const AttnArgs& a);
+void flash_bwd_dkv_t(const AttnArgs& a, const AttnDev& p, int heads_y, cudaStream_t s);
 
 }  // namespace himuon

@@ -45,8 +45,9 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x;   // heavy (late) query blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
+  int sblk, h, b;
+  attn_block_coords(sblk, h, b);
+  const int qb = gridDim.x - 1 - sblk;         // heavy (late) query blocks first
   const int hk = h / (p.Hq / p.Hkv);
   int nkv = (qb + 1) * (AT / BKV);             // KV blocks up to and including the diagonal
   const int nkv_all = (p.S + BKV - 1) / BKV;
@@ -252,8 +253,9 @@ flash_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  int sblk, h, b;
+  attn_block_coords(sblk, h, b);
+  const int qb = gridDim.x - 1 - sblk;         // heavy (late) query blocks first
   const int hk = h / (p.Hq / p.Hkv);
   int nkv = (qb + 1) * (AT / BKV);
   const int nkv_all = (p.S + BKV - 1) / BKV;

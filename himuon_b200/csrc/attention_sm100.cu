@@ -35,8 +35,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x;   // heavy (late) query blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
+  int sblk, h, b;
+  attn_block_coords(sblk, h, b);
+  const int qb = gridDim.x - 1 - sblk;         // heavy (late) query blocks first
   const int hk = h / (p.Hq / p.Hkv);
   const int nkv = qb + 1;
 
@@ -244,8 +245,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  int sblk, h, b;
+  attn_block_coords(sblk, h, b);
+  const int qb = gridDim.x - 1 - sblk;         // heavy (late) query blocks first
   const int hk = h / (p.Hq / p.Hkv);
   const int nkv = qb + 1;
 
@@ -403,15 +405,15 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb = blockIdx.x;
-  const int b = blockIdx.z;
-  // Grouped heads: either this CTA walks all G query heads of KV head blockIdx.y, or (split_heads) it handles the
-  // single query head blockIdx.y and its output is a per-head partial that a later pass sums over the group.
+  int kb, hy, b;
+  attn_block_coords(kb, hy, b);        // early KV blocks (attended by the most query blocks) start first
+  // Grouped heads: either this CTA walks all G query heads of KV head hy, or (split_heads) it handles the
+  // single query head hy and its output is a per-head partial that a later pass sums over the group.
   const int Gall = p.Hq / p.Hkv;
   const int G = p.split_heads ? 1 : Gall;
-  const int hk = p.split_heads ? blockIdx.y / Gall : blockIdx.y;
-  const int h_first = p.split_heads ? blockIdx.y : hk * Gall;
-  const int out_head = p.split_heads ? blockIdx.y : hk;
+  const int hk = p.split_heads ? hy / Gall : hy;
+  const int h_first = p.split_heads ? hy : hk * Gall;
+  const int out_head = p.split_heads ? hy : hk;
   const int nq = p.nblk - kb;          // query blocks kb .. nblk-1
   const int iters = G * nq;
 
@@ -624,10 +626,13 @@ void flash_attn_bwd(const AttnArgs& a, cudaStream_t s) {
     AttnDev ps = p;
     ps.split_heads = 1;
     ps.dk = a.dk_part; ps.dv = a.dv_part; ps.ld_dk = a.ld_part; ps.ld_dv = a.ld_part;
-    flash_bwd_dkv_kernel<<<dim3(p.nblk, a.Hq, a.B), 192, SMEM_DKV, s>>>(tq, tk, tv, tdo, ps);
+    if (flash_bwd_dkv_t_supported(a)) flash_bwd_dkv_t(a, ps, a.Hq, s);
+    else flash_bwd_dkv_kernel<<<dim3(p.nblk, a.Hq, a.B), 192, SMEM_DKV, s>>>(tq, tk, tv, tdo, ps);
     const long long tokens = static_cast<long long>(a.B) * a.S;
     group_sum_heads(a.dk_part, a.dk, tokens, a.Hkv, G, a.ld_part, a.ld_dk, s);
     group_sum_heads(a.dv_part, a.dv, tokens, a.Hkv, G, a.ld_part, a.ld_dv, s);
+  } else if (flash_bwd_dkv_t_supported(a)) {
+    flash_bwd_dkv_t(a, p, a.Hkv, s);
   } else {
     flash_bwd_dkv_kernel<<<dim3(p.nblk, a.Hkv, a.B), 192, SMEM_DKV, s>>>(tq, tk, tv, tdo, p);
   }

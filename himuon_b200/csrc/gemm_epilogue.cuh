@@ -21,6 +21,7 @@ struct GemmDev {
   // `nslices` (2..4) K-ranges, one item each, whose fp32 partial sums meet in `ws`; the slice that arrives last
   // adds the others to its accumulator and runs the epilogue.
   int full_items, total_items, nslices, split_debug;
+  int reduce_out;   // pair kernel, fp32 C += alpha*acc (aux == C, beta == 1): whole tiles add into C with TMA reductions
   float* ws;        // one-CTA kernel: [tail tile][slice][BM][BN] fp32; pair kernel: [tail tile][256][256] fp32 running sums
   int* counters;    // arrivals per tail tile (self-resetting)
   int* status;
