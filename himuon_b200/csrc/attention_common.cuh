@@ -80,5 +80,7 @@ void flash_bwd_dq_kv64(const AttnArgs& a, cudaStream_t s);
 // dK/dV pass in the transposed formulation (P^T and dS^T stay in tensor memory); S must be a multiple of 128.
 bool flash_bwd_dkv_t_supported(const AttnArgs& a);
 void flash_bwd_dkv_t(const AttnArgs& a, const AttnDev& p, int heads_y, cudaStream_t s);
+bool flash_bwd_dq_t_supported(const AttnArgs& a);
+void flash_bwd_dq_t(const AttnArgs& a, const AttnDev& p, cudaStream_t s);
 
 }  // namespace himuon

@@ -617,7 +617,8 @@ void flash_attn_bwd(const AttnArgs& a, cudaStream_t s) {
   p.status = status_word_ptr();
   const CUtensorMap tq = head_tmap(a.q, a.B, a.S, a.Hq, a.ld_q), tk = head_tmap(a.k, a.B, a.S, a.Hkv, a.ld_k),
                     tv = head_tmap(a.v, a.B, a.S, a.Hkv, a.ld_v), tdo = head_tmap(a.d_o, a.B, a.S, a.Hq, a.ld_do);
-  if (use_kv64()) flash_bwd_dq_kv64(a, s);
+  if (flash_bwd_dq_t_supported(a)) flash_bwd_dq_t(a, p, s);
+  else if (use_kv64()) flash_bwd_dq_kv64(a, s);
   else flash_bwd_dq_kernel<<<dim3(p.nblk, a.Hq, a.B), 192, SMEM_DQ, s>>>(tq, tk, tv, tdo, p);
   const int G = a.Hq / a.Hkv;
   if (G > 1 && a.dk_part != nullptr && a.dv_part != nullptr) {
