@@ -21,10 +21,14 @@ namespace himuon {
 
 __device__ int g_status_word = 0;
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+// AUX_TMA (bf16 output with an aux operand): the aux tile arrives by TMA in the very staging slab that its output slab
+// leaves from.  Four slabs rotate through load -> combine in place -> store, with the load issued two slabs ahead
+// (across tile boundaries), so the epilogue threads never wait on global memory.
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool AUX_TMA = false>
 __global__ void __launch_bounds__(256, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, GemmDev p) {
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX, GemmDev p) {
+  constexpr int NSTG = AUX_TMA ? 4 : 2;       // staging slabs
   constexpr uint32_t A_BYTES = BM * BK * 2;
   constexpr uint32_t B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -33,12 +37,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align_up_1024(smem_raw);
   uint8_t* sC = smem + STAGES * STAGE_BYTES;                      // two staging slabs for the TMA-store epilogue
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sC + 2 * SLAB_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sC + NSTG * SLAB_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
   uint64_t* tfull = bars + 2 * STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* aux_full = tempty + 2;            // AUX_TMA: one per staging slab
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_full + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = abort_flag + 1;
 
@@ -54,6 +59,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&tfull[a], 1);
       mbar_init(&tempty[a], 4);
     }
+    for (int a = 0; a < 4; ++a) mbar_init(&aux_full[a], 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -147,6 +153,93 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t slab_seq = 0;
     const bool issuer = (threadIdx.x == 128);
     if (issuer && p.tma_store) tma_prefetch_desc(&tmC);
+    if constexpr (AUX_TMA) {
+      constexpr int SW = 64, SLABS = BN / SW;
+      const int row_in_tile = ew * 32 + lane;
+      // Prefetch cursor (issuer only): the (tile, slab) pairs of this CTA in the order the epilogue visits them.
+      int pf_item = blockIdx.x, pf_sl = 0;
+      uint32_t pf_seq = 0;
+      auto prefetch_next = [&]() {
+        while (pf_item < p.total_items) {
+          const int b = pf_item / tiles_per_batch;
+          const int r = pf_item - b * tiles_per_batch;
+          const int mt = r % p.tiles_m;
+          const int nt = r / p.tiles_m;
+          const int col = nt * BN + pf_sl * SW;
+          if (col < p.N) {
+            const uint32_t buf = pf_seq & 3;
+            mbar_expect_tx(&aux_full[buf], SLAB_BYTES);
+            tma_load_3d(sC + buf * SLAB_BYTES, &tmX, &aux_full[buf], col, mt * BM, b);
+            ++pf_seq;
+            if (++pf_sl == SLABS) { pf_sl = 0; pf_item += gridDim.x; }
+            return;
+          }
+          pf_sl = 0;                         // the rest of this tile lies past N
+          pf_item += gridDim.x;
+        }
+      };
+      if (issuer) {
+        tma_prefetch_desc(&tmX);
+        prefetch_next();
+        prefetch_next();
+      }
+      uint32_t g = 0;                        // slabs finished by this CTA
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
+        const int b = item / tiles_per_batch;
+        const int r = item - b * tiles_per_batch;
+        const int mt = r % p.tiles_m;
+        const int nt = r / p.tiles_m;
+        if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, p.status, 3)) break;
+        tc_fence_after();
+        const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+        for (int sl = 0; sl < SLABS; ++sl) {
+          const int col = nt * BN + sl * SW;
+          if (col >= p.N) break;             // uniform over the 128 threads
+          const uint32_t buf = g & 3;
+          uint8_t* my_row = sC + buf * SLAB_BYTES + row_in_tile * 128;
+          if (!mbar_wait(&aux_full[buf], (g >> 2) & 1, abort_flag, p.status, 5)) { ok = false; break; }
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            uint32_t v[32];
+            tmem_ld32(t_acc + sl * SW + ch * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4* cell = reinterpret_cast<uint4*>(my_row + (((ch * 4 + q) ^ (row_in_tile & 7)) << 4));
+              const uint4 e = *cell;
+              const uint32_t ew4[4] = {e.x, e.y, e.z, e.w};
+              uint32_t o[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                float f0 = p.alpha * __uint_as_float(v[8 * q + 2 * t]);
+                float f1 = p.alpha * __uint_as_float(v[8 * q + 2 * t + 1]);
+                if (p.round_acc) { f0 = round_bf16(f0); f1 = round_bf16(f1); }
+                o[t] = pack_bf16x2(f0 + p.beta * bf16_lo(ew4[t]), f1 + p.beta * bf16_hi(ew4[t]));
+              }
+              *cell = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+          fence_proxy_async_smem();
+          named_barrier(1, 128);             // the whole slab is combined
+          if (issuer) {
+            tma_store_3d(&tmC, sC + buf * SLAB_BYTES, col, mt * BM, b);
+            tma_store_commit();
+            tma_store_wait_read<1>();        // the slab stored before this one is drained: its buffer takes slab g+2
+            prefetch_next();
+          }
+          ++g;
+        }
+        if (!ok) break;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+      if (issuer) tma_store_wait_read<0>();
+    } else
     for (int item = blockIdx.x; item < p.total_items; item += gridDim.x) {
       const WorkItem w = decode_item(p, item);
       const int tile = w.tile;
@@ -301,7 +394,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
-    if (issuer && p.tma_store) tma_store_wait_read<0>();   // no store may still be reading shared memory at exit
+    if (!AUX_TMA && issuer && p.tma_store) tma_store_wait_read<0>();   // no store may still be reading shared memory at exit
   }
 
   tc_fence_before();
@@ -362,12 +455,23 @@ static SplitWorkspace& split_workspace() {
   return w;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+// bf16 output with a bf16 aux tile that TMA can fetch (16-byte aligned base, rows and batches)
+static bool aux_tma_ok(const GemmArgs& a) {
+  static const bool enabled = [] {
+    const char* e = getenv("HIMUON_GEMM_AUX_TMA");
+    return !(e && std::string(e) == "0");
+  }();
+  return enabled && a.aux != nullptr && !a.out_fp32 && a.ldaux % 8 == 0 && (a.batch == 1 || a.strideAux % 8 == 0) &&
+         reinterpret_cast<uintptr_t>(a.aux) % 16 == 0 && a.ldc % 8 == 0 && (a.batch == 1 || a.strideC % 8 == 0) &&
+         reinterpret_cast<uintptr_t>(a.C) % 16 == 0;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool AUX_TMA = false>
 static void launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * 2;
-  constexpr size_t SMEM = 1024 + STAGES * STAGE_BYTES + 2 * SLAB_BYTES + 256;
+  constexpr size_t SMEM = 1024 + STAGES * STAGE_BYTES + (AUX_TMA ? 4 : 2) * SLAB_BYTES + 256;
   static_assert(SMEM <= 232448, "shared memory budget of one CTA exceeded");
-  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, AUX_TMA>;
   static bool attr_done = false;
   if (!attr_done) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM));
@@ -389,7 +493,7 @@ static void launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   CUtensorMap tmA = make_tmap(a.A, 3, dimsA, strA, boxA, 2, true);
   CUtensorMap tmB = make_tmap(a.B, 3, dimsB, strB, boxB, 2, true);
 
-  GemmDev p;
+  GemmDev p{};
   p.C = a.C; p.aux = a.aux;
   p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
   p.ldc = a.ldc; p.ldaux = a.ldaux; p.strideC = a.strideC; p.strideAux = a.strideAux;
@@ -412,6 +516,14 @@ static void launch_gemm(const GemmArgs& a, cudaStream_t stream) {
     const uint32_t boxC[3] = {static_cast<uint32_t>(128 / esz), BM, 1};
     tmC = make_tmap(a.C, 3, dimsC, strC, boxC, esz, true);
   }
+  CUtensorMap tmX = tmC;
+  if (AUX_TMA) {
+    const uint64_t dimsX[3] = {static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.M), static_cast<uint64_t>(a.batch)};
+    const uint64_t strX[2] = {static_cast<uint64_t>(a.ldaux) * 2,
+                              a.batch > 1 ? static_cast<uint64_t>(a.strideAux) * 2 : static_cast<uint64_t>(a.ldaux) * 2 * a.M};
+    const uint32_t boxX[3] = {64, BM, 1};
+    tmX = make_tmap(a.aux, 3, dimsX, strX, boxX, 2, true);
+  }
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batch;
   int sms = a.max_ctas > 0 ? a.max_ctas : num_sms();
   // Split-K for the last wave when it would leave more than half of the SMs idle.
@@ -421,7 +533,7 @@ static void launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   p.ws = nullptr;
   p.counters = nullptr;
   const int rem = static_cast<int>(total % sms);
-  if (p.tma_store && !tuning().no_split && rem > 0 && rem * 2 <= sms && p.kblocks >= 16) {
+  if (!AUX_TMA && p.tma_store && !tuning().no_split && rem > 0 && rem * 2 <= sms && p.kblocks >= 16) {
     int sl = sms / rem;
     if (sl > p.kblocks / 8) sl = p.kblocks / 8;
     if (sl > tuning().split_max) sl = tuning().split_max;   // the last slice reads (sl - 1) x 128 KB of partials
@@ -435,7 +547,7 @@ static void launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   }
   p.total_items = p.full_items + (p.nslices > 1 ? rem * p.nslices : 0);
   const int grid = static_cast<int>(p.total_items < sms ? p.total_items : sms);
-  kern<<<grid, 256, SMEM, stream>>>(tmA, tmB, tmC, p);
+  kern<<<grid, 256, SMEM, stream>>>(tmA, tmB, tmC, tmX, p);
 }
 
 int num_sms() {
@@ -466,7 +578,14 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     case 2: launch_gemm<BN_, ST_, true, false>(a, stream); break;                  \
     default: launch_gemm<BN_, ST_, true, true>(a, stream); break;                  \
   }
-  if (best_bn == 128) { HM_LAUNCH(128, 6) }
+  if (best_bn == 256 && !tuning().force_direct && aux_tma_ok(a)) {
+    switch (sel) {
+      case 0: launch_gemm<256, 3, false, false, true>(a, stream); break;
+      case 1: launch_gemm<256, 3, false, true, true>(a, stream); break;
+      case 2: launch_gemm<256, 3, true, false, true>(a, stream); break;
+      default: launch_gemm<256, 3, true, true, true>(a, stream); break;
+    }
+  } else if (best_bn == 128) { HM_LAUNCH(128, 6) }
   else if (best_bn == 192) { HM_LAUNCH(192, 4) }
   else { HM_LAUNCH(256, 4) }
 #undef HM_LAUNCH
