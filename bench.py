@@ -49,6 +49,8 @@ def parse():
     p.add_argument("--grad-acc", type=int, default=GRAD_ACC)
     p.add_argument("--tile", type=int, default=TILE)
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-step-graph", action="store_true",
+                   help="run forward/backward eagerly instead of replaying the captured micro-batch CUDA graphs")
     p.add_argument("--engine", type=str, default="fsdp", choices=["fsdp", "ddp"],
                    help="fsdp: bank-sharded engine (headline); ddp: replicated parameters + fused all-reduce")
     p.add_argument("--optimizer", type=str, default="himuon", help="himuon | muon-fsdp | muon | adamw (headline: himuon)")
@@ -137,7 +139,8 @@ def run_ours(args):
     if args.engine == "fsdp":
         engine.attach_optimizer(optimizer)
     scheduler = wsd_schedule(optimizer, 100, 0, 400, 0.1)
-    trainer = Trainer(model, optimizer, scheduler, engine, args.grad_acc, device)
+    trainer = Trainer(model, optimizer, scheduler, engine, args.grad_acc, device,
+                      graph_microbatch=not args.no_step_graph, graph_warmup_steps=min(2, max(1, args.warmup - 1)))
     trainer.zero_set_to_none = False
     model.train()
 
@@ -198,6 +201,7 @@ def run_ours(args):
                        "seq_len": args.seq_len, "micro_batch_per_gpu": args.micro_batch, "grad_acc": args.grad_acc,
                        "parallelism": f"fsdp-banks{world}" if args.engine == "fsdp" else f"dp{world}",
                        "optimizer": f"{args.optimizer} tile {args.tile}, lr {ns.lr}, wd {WD}, cuda graph",
+                       "forward_backward": "eager" if args.no_step_graph else "micro-batch CUDA graphs (public Trainer option)",
                        "activation_checkpointing": False,
                        "l2": "no flush: each step streams >8 GB of weights and activations (L2 is 126 MB)"},
             "optimizer_step_ms": opt_ms,

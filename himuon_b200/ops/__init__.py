@@ -11,6 +11,8 @@ from __future__ import annotations
 
 import math
 
+import weakref
+
 import torch
 
 from . import reference as ref
@@ -26,6 +28,11 @@ def launch_count() -> int:
 def _count(n: int = 1) -> None:
     global _LAUNCHES
     _LAUNCHES += n
+
+
+def add_launches(n: int) -> None:
+    """Accounts for kernels launched by replaying a captured CUDA graph (the Python wrappers do not run then)."""
+    _count(n)
 
 
 def use_kernels(t: torch.Tensor) -> bool:
@@ -80,11 +87,19 @@ class GradSink:
     buffer).  The first write after ``reset()`` overwrites, later writes accumulate.
     """
 
-    __slots__ = ("buffer", "fresh")
+    __slots__ = ("buffer", "fresh", "__weakref__")
+    _all: "weakref.WeakSet[GradSink]" = weakref.WeakSet()
 
     def __init__(self, buffer: torch.Tensor):
         self.buffer = buffer
         self.fresh = True
+        GradSink._all.add(self)
+
+    @classmethod
+    def mark_all_used(cls) -> None:
+        """After a replayed CUDA graph wrote the first micro-batch's gradients (no Python ran): later writes add."""
+        for s in cls._all:
+            s.fresh = False
 
     def reset(self):
         self.fresh = True

@@ -52,6 +52,8 @@ def build_arg_parser(mode: str) -> argparse.ArgumentParser:
                    help='JSON list such as \'[{"step": 0, "tile_size": 1000000000}, {"step": 200, "tile_size": 512}]\'')
     p.add_argument("--cuda-graph", dest="cuda_graph", action=argparse.BooleanOptionalAction,
                    default=(mode != "fsdp"))
+    p.add_argument("--cuda-graph-step", dest="cuda_graph_step", action="store_true",
+                   help="replay forward+backward of each micro-batch from captured CUDA graphs (static batch shapes)")
     p.add_argument("--time-budget", type=float, default=None, help="hours")
     p.add_argument("--eval-interval", type=int, default=0)
     p.add_argument("--eval-steps", type=int, default=10)
@@ -156,7 +158,7 @@ class Trainer:
     """
 
     def __init__(self, model, optimizer, scheduler=None, engine=None, grad_acc: int = 1, device=None,
-                 autocast_dtype=None):
+                 autocast_dtype=None, graph_microbatch: bool = False, graph_warmup_steps: int = 2):
         self.model, self.optimizer, self.scheduler, self.engine = model, optimizer, scheduler, engine
         self.grad_acc = int(grad_acc)
         self.device = device if device is not None else next(model.parameters()).device
@@ -166,6 +168,57 @@ class Trainer:
             model.set_loss_scale(1.0 / self.grad_acc)
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        # Optional: forward+backward of one micro-batch replayed from a CUDA graph (removes ~30k kernel launches'
+        # worth of host work per step).  Two graphs are captured after `graph_warmup_steps` eager steps: one for
+        # the first micro-batch of a step (weight gradients overwrite) and one for the others (they accumulate).
+        # Needs static shapes and gradients that are zeroed in place, never dropped.
+        self.graph_microbatch = bool(graph_microbatch) and self.device.type == "cuda"
+        self.graph_warmup_steps = int(graph_warmup_steps)
+        self._steps_done = 0
+        self._mb_graphs = {}          # first(bool) -> (graph, static loss, launches)
+        self._mb_static = None
+        self._mb_pool = None
+        if self.graph_microbatch:
+            self.zero_set_to_none = False
+
+    # ------------------------------------------------------------------ micro-batch forward + backward
+    def _eager_microbatch(self, batch, sync: bool) -> torch.Tensor:
+        ctx = self.engine.no_sync() if (self.engine is not None and not sync) else nullcontext()
+        with ctx:
+            loss = self.model(batch["input_ids"], labels=batch["labels"]).loss
+            (loss / self.grad_acc).backward()
+        return loss.detach()
+
+    def _graph_microbatch(self, batch, first: bool, sync: bool) -> torch.Tensor:
+        from . import ops
+
+        ids, labels = batch["input_ids"], batch["labels"]
+        usable = (self._steps_done >= self.graph_warmup_steps and self.model.training and not self.zero_set_to_none
+                  and (self._mb_static is None or (self._mb_static["input_ids"].shape == ids.shape
+                                                   and self._mb_static["labels"].shape == labels.shape)))
+        if not usable:
+            return self._eager_microbatch(batch, sync)
+        if self._mb_static is None:
+            self._mb_static = {"input_ids": torch.empty_like(ids), "labels": torch.empty_like(labels)}
+        self._mb_static["input_ids"].copy_(ids)
+        self._mb_static["labels"].copy_(labels)
+        entry = self._mb_graphs.get(first)
+        if entry is None:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            n0 = ops.launch_count()
+            with torch.cuda.graph(graph, pool=self._mb_pool):
+                loss = self.model(self._mb_static["input_ids"], labels=self._mb_static["labels"]).loss
+                (loss / self.grad_acc).backward()
+                static_loss = loss.detach()
+            self._mb_pool = graph.pool()
+            entry = (graph, static_loss, ops.launch_count() - n0)     # the capture ran the wrappers once: counted
+            self._mb_graphs[first] = entry
+        else:
+            ops.add_launches(entry[2])
+        entry[0].replay()
+        ops.GradSink.mark_all_used()
+        return entry[1].clone()
 
     def _to_device(self, batch):
         out = {}
@@ -181,11 +234,11 @@ class Trainer:
         for i, hb in enumerate(host_batches):
             batch = self._to_device(hb)
             sync = i == self.grad_acc - 1
-            ctx = self.engine.no_sync() if (self.engine is not None and not sync) else nullcontext()
-            with ctx:
-                loss = self.model(batch["input_ids"], labels=batch["labels"]).loss
-                (loss / self.grad_acc).backward()
-            total = loss.detach() if total is None else total + loss.detach()
+            if self.graph_microbatch:
+                loss = self._graph_microbatch(batch, first=(i == 0), sync=sync)
+            else:
+                loss = self._eager_microbatch(batch, sync)
+            total = loss if total is None else total + loss
         if self.engine is not None:
             self.engine.finish_backward()
         self.optimizer.step()
@@ -195,6 +248,7 @@ class Trainer:
             self.engine.zero_grad(set_to_none=self.zero_set_to_none)
         else:
             self.optimizer.zero_grad(set_to_none=self.zero_set_to_none)
+        self._steps_done += 1
         return total / self.grad_acc
 
     def read_loss(self, loss: torch.Tensor) -> float:
@@ -285,7 +339,8 @@ def run_training(args, mode: str) -> dict:
     apply_reconfigure = make_apply_reconfigure(optimizer, parse_reconfigure_schedule(args.reconfigure_schedule), log)
     apply_reconfigure(0)
 
-    trainer = Trainer(model, optimizer, scheduler, engine, args.gradient_accumulation_steps, device)
+    trainer = Trainer(model, optimizer, scheduler, engine, args.gradient_accumulation_steps, device,
+                      graph_microbatch=bool(getattr(args, "cuda_graph_step", False)))
     trainer.zero_set_to_none = not args.cuda_graph if hasattr(optimizer, "reconfigure") else True
     budget = TimeBudget(args.time_budget)
     eos = getattr(tokenizer, "eos_token_id", None)
