@@ -120,7 +120,9 @@ static void headnorm_rope_fwd(const at::Tensor& x, const c10::optional<at::Tenso
   HM_CHECK(x.is_cuda() && is_bf16(x) && is_bf16(y) && x.dim() == 2 && y.dim() == 2 && x.stride(1) == 1 && y.stride(1) == 1, "headnorm_rope_fwd: bad tensors");
   HM_CHECK(x.size(1) == heads * 128 && y.size(1) == heads * 128, "headnorm_rope_fwd: head_dim must be 128");
   HM_CHECK(is_f32(cos_sin) && cos_sin.is_contiguous() && cos_sin.numel() >= seq_len * 128, "headnorm_rope_fwd: bad rope table");
-  HM_CHECK(x.stride(0) % 2 == 0 && y.stride(0) % 2 == 0, "headnorm_rope_fwd: row strides must be even");
+  HM_CHECK(x.stride(0) % 8 == 0 && y.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0 &&
+               reinterpret_cast<uintptr_t>(y.data_ptr()) % 16 == 0,
+           "headnorm_rope_fwd: rows must start on 16-byte boundaries");
   const bool use_norm = w.has_value();
   if (use_norm) HM_CHECK(rstd.has_value() && rstd->numel() >= x.size(0) * heads && is_bf16(*w) && w->numel() == 128, "headnorm_rope_fwd: norm needs weight[128] and rstd");
   const c10::cuda::CUDAGuard guard(x.device());
@@ -133,6 +135,10 @@ static void headnorm_rope_bwd(const at::Tensor& dy, const c10::optional<at::Tens
                               const at::Tensor& cos_sin, int64_t heads, int64_t seq_len) {
   HM_CHECK(dy.is_cuda() && is_bf16(dy) && is_bf16(dx) && dy.dim() == 2 && dx.dim() == 2 && dy.stride(1) == 1 && dx.stride(1) == 1, "headnorm_rope_bwd: bad tensors");
   HM_CHECK(dy.size(1) == heads * 128 && dx.size(1) == heads * 128, "headnorm_rope_bwd: head_dim must be 128");
+  HM_CHECK(dy.stride(0) % 8 == 0 && dx.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(dy.data_ptr()) % 16 == 0 &&
+               reinterpret_cast<uintptr_t>(dx.data_ptr()) % 16 == 0 &&
+               (!x.has_value() || (x->stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(x->data_ptr()) % 16 == 0)),
+           "headnorm_rope_bwd: rows must start on 16-byte boundaries");
   const bool use_norm = w.has_value();
   if (use_norm) HM_CHECK(x.has_value() && rstd.has_value() && dw_accum.has_value() && is_f32(*dw_accum) && dw_accum->numel() == 128 && x->stride(1) == 1, "headnorm_rope_bwd: norm needs x, rstd, dw_accum");
   const c10::cuda::CUDAGuard guard(dy.device());

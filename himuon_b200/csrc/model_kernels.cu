@@ -158,7 +158,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 // with shuffles (no block-wide barrier per row) and accumulates its dw contribution in registers over all the rows
 // it processes (a lane always owns the same columns); dy is re-read for the second pass (it is still in L1).
 // Eight rows are in flight per block; the block flushes dw once through shared memory.
-template <int ITERS>      // ITERS * 32 lanes * 8 elements columns at most
+template <int ITERS, bool WITH_DW>      // ITERS * 32 lanes * 8 elements columns at most
 __global__ void __launch_bounds__(256)
 rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                         const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -197,8 +197,10 @@ rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
           const float xh0 = bf16_lo(xu[q]) * rs, xh1 = bf16_hi(xu[q]) * rs;
           const float g0 = bf16_lo(gu[q]), g1 = bf16_hi(gu[q]);
           dot += g0 * bf16_lo(wu[q]) * xh0 + g1 * bf16_hi(wu[q]) * xh1;
-          dwp[a][2 * q] += g0 * xh0;
-          dwp[a][2 * q + 1] += g1 * xh1;
+          if (WITH_DW) {
+            dwp[a][2 * q] += g0 * xh0;
+            dwp[a][2 * q + 1] += g1 * xh1;
+          }
         }
       }
     }
@@ -222,7 +224,7 @@ rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
       }
     }
   }
-  if (dw_accum) {
+  if (WITH_DW && dw_accum) {
 #pragma unroll
     for (int a = 0; a < ITERS; ++a) {
       const int i = lane + a * 32;
@@ -233,6 +235,51 @@ rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
     }
     __syncthreads();
     for (int i = threadIdx.x; i < cols; i += blockDim.x) atomicAdd(dw_accum + i, s_dw[i]);
+  }
+}
+
+// dw of RMSNorm as a column-strip reduction: block (cb, rb) covers 256 columns x `rows_per_block` rows, one warp per
+// row at a time (a lane owns 8 adjacent columns), the eight warps meet in shared memory and each strip adds its sums
+// with four-wide atomics.  Run next to the warp-per-row dx kernel, it keeps the per-row pass free of dw state
+// (fewer registers, more rows in flight) and cuts the atomics per output cache line from thousands to a few hundred.
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_dw_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                      const float* __restrict__ rstd, float* __restrict__ dw_accum, int rows, int cols,
+                      int rows_per_block) {
+  __shared__ float part[8][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + lane * 8;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(rows, r0 + rows_per_block);
+  float acc[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+  if (col < cols) {
+#pragma unroll 4
+    for (int r = r0 + warp; r < r1; r += 8) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(x + static_cast<long long>(r) * cols + col);
+      const uint4 gv = *reinterpret_cast<const uint4*>(dy + static_cast<long long>(r) * cols + col);
+      const float rs = rstd[r];
+      const uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w}, gu[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        acc[2 * q] += bf16_lo(gu[q]) * (bf16_lo(xu[q]) * rs);
+        acc[2 * q + 1] += bf16_hi(gu[q]) * (bf16_hi(xu[q]) * rs);
+      }
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < 8; ++q) part[warp][lane * 8 + q] = acc[q];
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    const int c = threadIdx.x * 4;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) {
+      sum.x += part[w8][c]; sum.y += part[w8][c + 1]; sum.z += part[w8][c + 2]; sum.w += part[w8][c + 3];
+    }
+    const int gc = blockIdx.x * 256 + c;
+    if (gc + 3 < cols) atomicAdd(reinterpret_cast<float4*>(dw_accum + gc), sum);   // cols is a multiple of 8
   }
 }
 
@@ -255,9 +302,21 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
     auto xp = reinterpret_cast<const __nv_bfloat16*>(x);
     auto wp = reinterpret_cast<const __nv_bfloat16*>(w);
     auto dxp = reinterpret_cast<__nv_bfloat16*>(dx);
-    if (cols <= 10 * 256) rmsnorm_bwd_warp_kernel<10><<<grid, 256, smem, s>>>(dyp, xp, wp, rstd, dxp, dw_accum, rows, cols);
-    else if (cols <= 16 * 256) rmsnorm_bwd_warp_kernel<16><<<grid, 256, smem, s>>>(dyp, xp, wp, rstd, dxp, dw_accum, rows, cols);
-    else rmsnorm_bwd_warp_kernel<20><<<grid, 256, smem, s>>>(dyp, xp, wp, rstd, dxp, dw_accum, rows, cols);
+    // dw goes to its own column-strip kernel (when its four-wide atomics are aligned); the row pass then carries none
+    float* dw_rows = dw_accum;
+    if (dw_accum != nullptr && reinterpret_cast<uintptr_t>(dw_accum) % 16 == 0) {
+      const int rpb = 64;
+      rmsnorm_bwd_dw_kernel<<<dim3((cols + 255) / 256, (rows + rpb - 1) / rpb), 256, 0, s>>>(dyp, xp, rstd, dw_accum, rows, cols, rpb);
+      dw_rows = nullptr;
+    }
+    const int row_grid = dw_rows ? grid : blocks_needed;
+#define HM_RMS_BWD(IT_)                                                                                              \
+  if (dw_rows) rmsnorm_bwd_warp_kernel<IT_, true><<<row_grid, 256, smem, s>>>(dyp, xp, wp, rstd, dxp, dw_rows, rows, cols); \
+  else rmsnorm_bwd_warp_kernel<IT_, false><<<row_grid, 256, smem, s>>>(dyp, xp, wp, rstd, dxp, nullptr, rows, cols);
+    if (cols <= 10 * 256) { HM_RMS_BWD(10) }
+    else if (cols <= 16 * 256) { HM_RMS_BWD(16) }
+    else { HM_RMS_BWD(20) }
+#undef HM_RMS_BWD
     return;
   }
   const int grid = rows < num_sms() * 4 ? rows : num_sms() * 4;
@@ -267,44 +326,69 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
 }
 
 // ------------------------------------------------------------------------------------------------ head-norm + RoPE
-// One warp per (token, head) vector of 128 elements: lane l holds elements {2l, 2l+1} of the first
-// half (i.e. 4 values: first-half pair and the matching second-half pair).
+// Per-head RMSNorm (optional) + RoPE on (token, head) vectors of 128 elements.
 // cos_sin: (seq_len, 64, 2) fp32.  Rotate-half convention:
 //   y[i]      = xn[i]*cos[i] - xn[i+64]*sin[i]
 //   y[i+64]   = xn[i+64]*cos[i] + xn[i]*sin[i]
+// Layout of the two kernels below: sixteen lanes per head vector, lane l owning elements [8l, 8l+8) (one 16-byte
+// access); lanes 0-7 hold the first half, lanes 8-15 the second half, so the rotation partner of every element sits
+// at the same register index in lane l^8.  A warp therefore handles two vectors per pass.
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  f[0] = bf16_lo(u.x); f[1] = bf16_hi(u.x); f[2] = bf16_lo(u.y); f[3] = bf16_hi(u.y);
+  f[4] = bf16_lo(u.z); f[5] = bf16_hi(u.z); f[6] = bf16_lo(u.w); f[7] = bf16_hi(u.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+
 __global__ void __launch_bounds__(256)
 headnorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                          __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, const float* __restrict__ cos_sin,
                          long long n_vec, int heads, int seq_len, long long ld_in, long long ld_out, float eps,
                          int use_norm) {
-  const int lane = threadIdx.x & 31;
-  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  float w0 = 1.f, w1 = 1.f, w2 = 1.f, w3 = 1.f;
-  if (use_norm) {
-    const uint32_t a = reinterpret_cast<const uint32_t*>(w)[lane], b = reinterpret_cast<const uint32_t*>(w)[32 + lane];
-    w0 = bf16_lo(a); w1 = bf16_hi(a); w2 = bf16_lo(b); w3 = bf16_hi(b);
-  }
-  for (long long vi = warp0; vi < n_vec; vi += nwarps) {
-    const long long tok = vi / heads;
-    const int head = static_cast<int>(vi - tok * heads);
-    const int pos = static_cast<int>(tok % seq_len);
-    const __nv_bfloat16* xp = x + tok * ld_in + head * 128;
-    const uint32_t a = reinterpret_cast<const uint32_t*>(xp)[lane], b = reinterpret_cast<const uint32_t*>(xp)[32 + lane];
-    float x0 = bf16_lo(a), x1 = bf16_hi(a), x2 = bf16_lo(b), x3 = bf16_hi(b);
+  const int sub = threadIdx.x & 15;                       // lane within the half warp
+  const bool second = sub >= 8;
+  const long long hw0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const long long nhw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 4;
+  float wv[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) wv[q] = 1.f;
+  if (use_norm) unpack8(reinterpret_cast<const uint4*>(w)[sub], wv);
+  const long long n_iter = (n_vec + nhw - 1) / nhw;       // the same trip count for every lane (shuffles inside)
+  for (long long it = 0; it < n_iter; ++it) {
+    const long long vi = hw0 + it * nhw;
+    const bool live = vi < n_vec;
+    const uint32_t vi32 = live ? static_cast<uint32_t>(vi) : 0u;          // n_vec < 2^31 (checked by the launcher)
+    const uint32_t tok = vi32 / static_cast<uint32_t>(heads);
+    const int head = static_cast<int>(vi32 - tok * static_cast<uint32_t>(heads));
+    const int pos = static_cast<int>(tok % static_cast<uint32_t>(seq_len));
+    float xv[8];
+    unpack8(reinterpret_cast<const uint4*>(x + static_cast<long long>(tok) * ld_in + head * 128)[sub], xv);
+    const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + static_cast<long long>(pos) * 128 + (sub & 7) * 16);
+    const float4 c0 = cs4[0], c1 = cs4[1], c2 = cs4[2], c3 = cs4[3];   // (cos, sin) of this lane's eight frequencies
+    const float cs[16] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w, c2.x, c2.y, c2.z, c2.w, c3.x, c3.y, c3.z, c3.w};
     if (use_norm) {
-      const float ss = warp_sum(x0 * x0 + x1 * x1 + x2 * x2 + x3 * x3);
+      float ss = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) ss += xv[q] * xv[q];
+      ss = half_warp_sum(ss);
       const float rs = rsqrtf(ss * (1.f / 128.f) + eps);
-      if (lane == 0 && rstd) rstd[vi] = rs;
-      x0 = round_bf16(round_bf16(x0 * rs) * w0); x1 = round_bf16(round_bf16(x1 * rs) * w1);
-      x2 = round_bf16(round_bf16(x2 * rs) * w2); x3 = round_bf16(round_bf16(x3 * rs) * w3);
+      if (sub == 0 && live && rstd) rstd[vi] = rs;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) xv[q] = round_bf16(round_bf16(xv[q] * rs) * wv[q]);
     }
-    const float4 cs = reinterpret_cast<const float4*>(cos_sin + static_cast<long long>(pos) * 128)[lane];  // c0,s0,c1,s1
-    const float y0 = x0 * cs.x - x2 * cs.y, y2 = x2 * cs.x + x0 * cs.y;
-    const float y1 = x1 * cs.z - x3 * cs.w, y3 = x3 * cs.z + x1 * cs.w;
-    __nv_bfloat16* yp = y + tok * ld_out + head * 128;
-    reinterpret_cast<uint32_t*>(yp)[lane] = pack_bf16x2(y0, y1);
-    reinterpret_cast<uint32_t*>(yp)[32 + lane] = pack_bf16x2(y2, y3);
+    float out[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float other = __shfl_xor_sync(0xffffffffu, xv[q], 8);
+      out[q] = second ? xv[q] * cs[2 * q] + other * cs[2 * q + 1] : xv[q] * cs[2 * q] - other * cs[2 * q + 1];
+    }
+    if (live) reinterpret_cast<uint4*>(y + static_cast<long long>(tok) * ld_out + head * 128)[sub] = pack8(out);
   }
 }
 
@@ -314,48 +398,73 @@ headnorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
                          __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_accum,
                          const float* __restrict__ cos_sin, long long n_vec, int heads, int seq_len, long long ld_dy,
                          long long ld_x, long long ld_dx, int use_norm) {
-  __shared__ float sdw[128];
-  const int lane = threadIdx.x & 31;
-  if (threadIdx.x < 128) sdw[threadIdx.x] = 0.f;
-  __syncthreads();
-  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  float w0 = 1.f, w1 = 1.f, w2 = 1.f, w3 = 1.f;
-  if (use_norm) {
-    const uint32_t a = reinterpret_cast<const uint32_t*>(w)[lane], b = reinterpret_cast<const uint32_t*>(w)[32 + lane];
-    w0 = bf16_lo(a); w1 = bf16_hi(a); w2 = bf16_lo(b); w3 = bf16_hi(b);
-  }
-  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-  for (long long vi = warp0; vi < n_vec; vi += nwarps) {
-    const long long tok = vi / heads;
-    const int head = static_cast<int>(vi - tok * heads);
-    const int pos = static_cast<int>(tok % seq_len);
-    const __nv_bfloat16* gp = dy + tok * ld_dy + head * 128;
-    const uint32_t ga = reinterpret_cast<const uint32_t*>(gp)[lane], gb = reinterpret_cast<const uint32_t*>(gp)[32 + lane];
-    const float g0 = bf16_lo(ga), g1 = bf16_hi(ga), g2 = bf16_lo(gb), g3 = bf16_hi(gb);
-    const float4 cs = reinterpret_cast<const float4*>(cos_sin + static_cast<long long>(pos) * 128)[lane];
-    // transpose of the rotation
-    float d0 = g0 * cs.x + g2 * cs.y, d2 = g2 * cs.x - g0 * cs.y;
-    float d1 = g1 * cs.z + g3 * cs.w, d3 = g3 * cs.z - g1 * cs.w;
-    if (use_norm) {
-      const __nv_bfloat16* xp = x + tok * ld_x + head * 128;
-      const uint32_t xa = reinterpret_cast<const uint32_t*>(xp)[lane], xb = reinterpret_cast<const uint32_t*>(xp)[32 + lane];
-      const float rs = rstd[vi];
-      const float h0 = bf16_lo(xa) * rs, h1 = bf16_hi(xa) * rs, h2 = bf16_lo(xb) * rs, h3 = bf16_hi(xb) * rs;
-      a0 += d0 * h0; a1 += d1 * h1; a2 += d2 * h2; a3 += d3 * h3;
-      const float mean = warp_sum(d0 * w0 * h0 + d1 * w1 * h1 + d2 * w2 * h2 + d3 * w3 * h3) * (1.f / 128.f);
-      d0 = rs * (d0 * w0 - h0 * mean); d1 = rs * (d1 * w1 - h1 * mean);
-      d2 = rs * (d2 * w2 - h2 * mean); d3 = rs * (d3 * w3 - h3 * mean);
+  __shared__ float sdw[8][128];                         // one row of partial dw per warp
+  const int sub = threadIdx.x & 15;
+  const bool second = sub >= 8;
+  const long long hw0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const long long nhw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 4;
+  float wv[8], acc[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) { wv[q] = 1.f; acc[q] = 0.f; }
+  if (use_norm) unpack8(reinterpret_cast<const uint4*>(w)[sub], wv);
+  const long long n_iter = (n_vec + nhw - 1) / nhw;
+  for (long long it = 0; it < n_iter; ++it) {
+    const long long vi = hw0 + it * nhw;
+    const bool live = vi < n_vec;
+    const uint32_t vi32 = live ? static_cast<uint32_t>(vi) : 0u;          // n_vec < 2^31 (checked by the launcher)
+    const uint32_t tok = vi32 / static_cast<uint32_t>(heads);
+    const int head = static_cast<int>(vi32 - tok * static_cast<uint32_t>(heads));
+    const int pos = static_cast<int>(tok % static_cast<uint32_t>(seq_len));
+    float g[8];
+    unpack8(reinterpret_cast<const uint4*>(dy + static_cast<long long>(tok) * ld_dy + head * 128)[sub], g);
+    const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + static_cast<long long>(pos) * 128 + (sub & 7) * 16);
+    const float4 c0 = cs4[0], c1 = cs4[1], c2 = cs4[2], c3 = cs4[3];
+    const float cs[16] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w, c2.x, c2.y, c2.z, c2.w, c3.x, c3.y, c3.z, c3.w};
+    float d[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {                          // transpose of the rotation
+      const float other = __shfl_xor_sync(0xffffffffu, g[q], 8);
+      d[q] = second ? g[q] * cs[2 * q] - other * cs[2 * q + 1] : g[q] * cs[2 * q] + other * cs[2 * q + 1];
     }
-    __nv_bfloat16* op = dx + tok * ld_dx + head * 128;
-    reinterpret_cast<uint32_t*>(op)[lane] = pack_bf16x2(d0, d1);
-    reinterpret_cast<uint32_t*>(op)[32 + lane] = pack_bf16x2(d2, d3);
+    if (use_norm) {
+      float h[8];
+      unpack8(reinterpret_cast<const uint4*>(x + static_cast<long long>(tok) * ld_x + head * 128)[sub], h);
+      const float rs = live ? rstd[vi] : 0.f;
+      float dot = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        h[q] *= rs;
+        if (live) acc[q] += d[q] * h[q];
+        dot += d[q] * wv[q] * h[q];
+      }
+      const float mean = half_warp_sum(dot) * (1.f / 128.f);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) d[q] = rs * (d[q] * wv[q] - h[q] * mean);
+    }
+    if (live) reinterpret_cast<uint4*>(dx + static_cast<long long>(tok) * ld_dx + head * 128)[sub] = pack8(d);
   }
   if (use_norm && dw_accum) {
-    atomicAdd(&sdw[2 * lane], a0); atomicAdd(&sdw[2 * lane + 1], a1);
-    atomicAdd(&sdw[64 + 2 * lane], a2); atomicAdd(&sdw[64 + 2 * lane + 1], a3);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[q] += __shfl_xor_sync(0xffffffffu, acc[q], 16);   // the warp's two half warps
+    if ((threadIdx.x & 31) < 16) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) sdw[threadIdx.x >> 5][sub * 8 + q] = acc[q];
+    }
     __syncthreads();
-    if (threadIdx.x < 128) atomicAdd(dw_accum + threadIdx.x, sdw[threadIdx.x]);
+    if (threadIdx.x < 32) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int w8 = 0; w8 < 8; ++w8) {
+        v.x += sdw[w8][4 * threadIdx.x]; v.y += sdw[w8][4 * threadIdx.x + 1];
+        v.z += sdw[w8][4 * threadIdx.x + 2]; v.w += sdw[w8][4 * threadIdx.x + 3];
+      }
+      if (reinterpret_cast<uintptr_t>(dw_accum) % 16 == 0) {
+        atomicAdd(reinterpret_cast<float4*>(dw_accum) + threadIdx.x, v);   // 8 atomics per cache line and block
+      } else {
+        atomicAdd(dw_accum + 4 * threadIdx.x, v.x); atomicAdd(dw_accum + 4 * threadIdx.x + 1, v.y);
+        atomicAdd(dw_accum + 4 * threadIdx.x + 2, v.z); atomicAdd(dw_accum + 4 * threadIdx.x + 3, v.w);
+      }
+    }
   }
 }
 
@@ -363,7 +472,8 @@ void headnorm_rope_fwd(const void* x, const void* w, void* y, float* rstd, const
                        int seq_len, long long ld_in, long long ld_out, float eps, int use_norm, cudaStream_t s) {
   const long long n_vec = static_cast<long long>(tokens) * heads;
   if (n_vec <= 0) return;
-  const long long blocks = (n_vec + 7) / 8;
+  if (n_vec >= (1LL << 31)) throw std::runtime_error("himuon headnorm_rope: too many head vectors for one launch");
+  const long long blocks = (n_vec + 15) / 16;
   const int grid = static_cast<int>(blocks < num_sms() * 8 ? blocks : num_sms() * 8);
   headnorm_rope_fwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
                                                 reinterpret_cast<__nv_bfloat16*>(y), rstd, cos_sin, n_vec, heads, seq_len,
@@ -374,7 +484,8 @@ void headnorm_rope_bwd(const void* dy, const void* x, const void* w, const float
                        long long ld_dx, int use_norm, cudaStream_t s) {
   const long long n_vec = static_cast<long long>(tokens) * heads;
   if (n_vec <= 0) return;
-  const long long blocks = (n_vec + 7) / 8;
+  if (n_vec >= (1LL << 31)) throw std::runtime_error("himuon headnorm_rope: too many head vectors for one launch");
+  const long long blocks = (n_vec + 15) / 16;
   const int grid = static_cast<int>(blocks < num_sms() * 4 ? blocks : num_sms() * 4);
   headnorm_rope_bwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
                                                 reinterpret_cast<const __nv_bfloat16*>(w), rstd, reinterpret_cast<__nv_bfloat16*>(dx),
