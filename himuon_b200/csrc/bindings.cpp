@@ -96,22 +96,31 @@ static void adamw_step_advance(at::Tensor& step) {
   himuon::adamw_step_advance(step.data_ptr<float>(), cur_stream());
 }
 
-static void rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, at::Tensor& y, at::Tensor& rstd, double eps) {
+static void rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, at::Tensor& y, at::Tensor& rstd, double eps,
+                        const c10::optional<at::Tensor>& delta, const c10::optional<at::Tensor>& h_out) {
   HM_CHECK(x.is_cuda() && is_bf16(x) && is_bf16(w) && is_bf16(y) && is_f32(rstd) && x.is_contiguous() && y.is_contiguous(), "rmsnorm_fwd: bad tensors");
   const int cols = (int)x.size(-1);
   const int rows = (int)(x.numel() / cols);
   HM_CHECK(rstd.numel() >= rows && w.numel() == cols, "rmsnorm_fwd: shape mismatch");
+  HM_CHECK(delta.has_value() == h_out.has_value(), "rmsnorm_fwd: delta and h_out go together");
+  if (delta.has_value())
+    HM_CHECK(is_bf16(*delta) && is_bf16(*h_out) && delta->is_contiguous() && h_out->is_contiguous() &&
+                 delta->numel() == x.numel() && h_out->numel() == x.numel(), "rmsnorm_fwd: bad delta / h_out");
   const c10::cuda::CUDAGuard guard(x.device());
-  himuon::rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, cols, (float)eps, cur_stream());
+  himuon::rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, cols, (float)eps, cur_stream(),
+                      delta.has_value() ? delta->data_ptr() : nullptr, h_out.has_value() ? h_out->data_ptr() : nullptr);
 }
 static void rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w, const at::Tensor& rstd,
-                        at::Tensor& dx, at::Tensor& dw_accum) {
+                        at::Tensor& dx, at::Tensor& dw_accum, const c10::optional<at::Tensor>& dres) {
+  if (dres.has_value())
+    HM_CHECK(is_bf16(*dres) && dres->is_contiguous() && dres->numel() == x.numel(), "rmsnorm_bwd: bad residual gradient");
   HM_CHECK(dy.is_cuda() && is_bf16(dy) && is_bf16(x) && is_bf16(w) && is_bf16(dx) && is_f32(dw_accum) && dy.is_contiguous() && x.is_contiguous() && dx.is_contiguous(), "rmsnorm_bwd: bad tensors");
   const int cols = (int)x.size(-1);
   const int rows = (int)(x.numel() / cols);
   HM_CHECK(dw_accum.numel() == cols, "rmsnorm_bwd: dw_accum must have one fp32 per column");
   const c10::cuda::CUDAGuard guard(x.device());
-  himuon::rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), dw_accum.data_ptr<float>(), rows, cols, cur_stream());
+  himuon::rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), dw_accum.data_ptr<float>(), rows, cols, cur_stream(),
+                      dres.has_value() ? dres->data_ptr() : nullptr);
 }
 // x, y: (tokens, heads*128) views with unit inner stride and row stride ld
 static void headnorm_rope_fwd(const at::Tensor& x, const c10::optional<at::Tensor>& w, at::Tensor& y,
@@ -247,8 +256,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ns_normalize", &ns_normalize);
   m.def("adamw_multi", &adamw_multi);
   m.def("adamw_step_advance", &adamw_step_advance);
-  m.def("rmsnorm_fwd", &rmsnorm_fwd);
-  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("rstd"), py::arg("eps"),
+        py::arg("delta") = py::none(), py::arg("h_out") = py::none());
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("dx"),
+        py::arg("dw_accum"), py::arg("dres") = py::none());
   m.def("headnorm_rope_fwd", &headnorm_rope_fwd);
   m.def("headnorm_rope_bwd", &headnorm_rope_bwd);
   m.def("swiglu_fwd", &swiglu_fwd);

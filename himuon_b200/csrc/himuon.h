@@ -96,9 +96,12 @@ void adamw_multi(const AdamEntry* entries, int n_entries, long long total_units,
 void adamw_step_advance(float* step, cudaStream_t stream);
 
 // ---------------------------------------------------------------- model kernels
-void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s);
+// With `delta`/`h_out`: h_out = bf16(x + delta) is written and normalised instead of x (fused residual update).
+void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s,
+                 const void* delta = nullptr, void* h_out = nullptr);
+// With `dres` (same shape as dx): dx = dres + the norm's input gradient (the residual path's gradient joins here).
 void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_accum,
-                 int rows, int cols, cudaStream_t s);
+                 int rows, int cols, cudaStream_t s, const void* dres = nullptr);
 // Per-head RMSNorm (optional) + rotary embedding on a (tokens, heads, 128) view with row stride `ld`.
 void headnorm_rope_fwd(const void* x, const void* w, void* y, float* rstd, const float* cos_sin, int tokens,
                        int heads, int seq_len, long long ld_in, long long ld_out, float eps, int use_norm,

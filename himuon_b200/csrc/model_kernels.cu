@@ -51,13 +51,29 @@ __device__ __forceinline__ float block_max_f(float v, float* red) {
 
 // ------------------------------------------------------------------------------------------------ RMSNorm
 // One CTA per row; cols % 8 == 0.  y = bf16( bf16(x * rstd) * w )  (HF rounds to the input dtype before the weight).
+// With `delta` the row normalised is h = bf16(x + delta) (the residual update), which is also written to `h_out`:
+// the residual add and the norm that follows it share one pass.
+__device__ __forceinline__ uint4 add_bf16x8(const uint4& a, const uint4& b) {
+  const uint32_t au[4] = {a.x, a.y, a.z, a.w}, bu[4] = {b.x, b.y, b.z, b.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) o[q] = pack_bf16x2(bf16_lo(au[q]) + bf16_lo(bu[q]), bf16_hi(au[q]) + bf16_hi(bu[q]));
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
 __global__ void __launch_bounds__(256)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int cols, float eps) {
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int rows, int cols, float eps,
+                   const __nv_bfloat16* __restrict__ delta, __nv_bfloat16* __restrict__ h_out) {
   __shared__ float red[32];
   const int nv = cols >> 3;
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long long>(r) * cols);
+    if (delta != nullptr) {
+      const uint4* dr = reinterpret_cast<const uint4*>(delta + static_cast<long long>(r) * cols);
+      uint4* hr = reinterpret_cast<uint4*>(h_out + static_cast<long long>(r) * cols);
+      for (int i = threadIdx.x; i < nv; i += blockDim.x) hr[i] = add_bf16x8(xr[i], dr[i]);
+      xr = hr;                              // each thread re-reads only what it wrote itself
+    }
     float ss = 0.f;
     for (int i = threadIdx.x; i < nv; i += blockDim.x) {
       const uint4 v = xr[i];
@@ -90,7 +106,8 @@ constexpr int kNormColIters = 8;
 __global__ void __launch_bounds__(256)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
-                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_accum, int rows, int cols) {
+                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_accum, int rows, int cols,
+                   const __nv_bfloat16* __restrict__ dres) {
   __shared__ float red[32];
   const int nv = cols >> 3;
   float dwp[kNormColIters][8];
@@ -138,7 +155,10 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
           o[q] = pack_bf16x2(rs * (bf16_lo(gu[q]) * bf16_lo(wu[q]) - xh0 * mean),
                              rs * (bf16_hi(gu[q]) * bf16_hi(wu[q]) - xh1 * mean));
         }
-        dr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+        if (dres != nullptr)                  // gradient arriving on the residual path joins here
+          ov = add_bf16x8(ov, reinterpret_cast<const uint4*>(dres + static_cast<long long>(r) * cols)[i]);
+        dr[i] = ov;
       }
     }
   }
@@ -162,7 +182,8 @@ template <int ITERS, bool WITH_DW>      // ITERS * 32 lanes * 8 elements columns
 __global__ void __launch_bounds__(256)
 rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                         const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
-                        __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_accum, int rows, int cols) {
+                        __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_accum, int rows, int cols,
+                        const __nv_bfloat16* __restrict__ dres) {
   extern __shared__ float s_dw[];
   const int nv = cols >> 3;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -220,7 +241,10 @@ rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
           o[q] = pack_bf16x2(rs * (bf16_lo(gu[q]) * bf16_lo(wu[q]) - xh0 * mean),
                              rs * (bf16_hi(gu[q]) * bf16_hi(wu[q]) - xh1 * mean));
         }
-        dr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+        if (dres != nullptr)                  // gradient arriving on the residual path joins here
+          ov = add_bf16x8(ov, reinterpret_cast<const uint4*>(dres + static_cast<long long>(r) * cols)[i]);
+        dr[i] = ov;
       }
     }
   }
@@ -283,15 +307,19 @@ rmsnorm_bwd_dw_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
   }
 }
 
-void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s) {
+void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s,
+                 const void* delta, void* h_out) {
   if (rows <= 0) return;
   if (cols % 8) throw std::runtime_error("himuon rmsnorm: hidden size must be a multiple of 8");
+  if ((delta == nullptr) != (h_out == nullptr)) throw std::runtime_error("himuon rmsnorm: delta and h_out go together");
   const int grid = rows < num_sms() * 8 ? rows : num_sms() * 8;
   rmsnorm_fwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
-                                          reinterpret_cast<__nv_bfloat16*>(y), rstd, rows, cols, eps);
+                                          reinterpret_cast<__nv_bfloat16*>(y), rstd, rows, cols, eps,
+                                          reinterpret_cast<const __nv_bfloat16*>(delta), reinterpret_cast<__nv_bfloat16*>(h_out));
 }
 void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw_accum, int rows,
-                 int cols, cudaStream_t s) {
+                 int cols, cudaStream_t s, const void* dres) {
+  auto drp = reinterpret_cast<const __nv_bfloat16*>(dres);
   if (rows <= 0) return;
   if (cols % 8 || cols > 8 * 256 * kNormColIters) throw std::runtime_error("himuon rmsnorm_bwd: unsupported hidden size");
   if (cols <= 20 * 256) {
@@ -311,8 +339,8 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
     }
     const int row_grid = dw_rows ? grid : blocks_needed;
 #define HM_RMS_BWD(IT_)                                                                                              \
-  if (dw_rows) rmsnorm_bwd_warp_kernel<IT_, true><<<row_grid, 256, smem, s>>>(dyp, xp, wp, rstd, dxp, dw_rows, rows, cols); \
-  else rmsnorm_bwd_warp_kernel<IT_, false><<<row_grid, 256, smem, s>>>(dyp, xp, wp, rstd, dxp, nullptr, rows, cols);
+  if (dw_rows) rmsnorm_bwd_warp_kernel<IT_, true><<<row_grid, 256, smem, s>>>(dyp, xp, wp, rstd, dxp, dw_rows, rows, cols, drp); \
+  else rmsnorm_bwd_warp_kernel<IT_, false><<<row_grid, 256, smem, s>>>(dyp, xp, wp, rstd, dxp, nullptr, rows, cols, drp);
     if (cols <= 10 * 256) { HM_RMS_BWD(10) }
     else if (cols <= 16 * 256) { HM_RMS_BWD(16) }
     else { HM_RMS_BWD(20) }
@@ -322,7 +350,7 @@ void rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd
   const int grid = rows < num_sms() * 4 ? rows : num_sms() * 4;
   rmsnorm_bwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
                                           reinterpret_cast<const __nv_bfloat16*>(w), rstd, reinterpret_cast<__nv_bfloat16*>(dx),
-                                          dw_accum, rows, cols);
+                                          dw_accum, rows, cols, drp);
 }
 
 // ------------------------------------------------------------------------------------------------ head-norm + RoPE

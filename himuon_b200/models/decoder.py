@@ -108,9 +108,14 @@ class DecoderLayer(nn.Module):
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
 
-    def forward(self, h2d, B: int, S: int, cos_sin):
-        h2d = h2d + self.self_attn(self.input_layernorm(h2d), B, S, cos_sin)
-        return h2d + self.mlp(self.post_attention_layernorm(h2d))
+    def forward(self, h2d, delta, B: int, S: int, cos_sin):
+        """``delta`` is the previous block's output that has not been added to the residual stream yet (``None``
+        for the first layer): every residual add is fused with the RMSNorm that follows it.  Returns the updated
+        stream and this layer's own pending MLP output."""
+        h2d, n1 = ops.add_rmsnorm(h2d, delta, self.input_layernorm.weight, self.input_layernorm.variance_epsilon)
+        a = self.self_attn(n1, B, S, cos_sin)
+        h2d, n2 = ops.add_rmsnorm(h2d, a, self.post_attention_layernorm.weight, self.post_attention_layernorm.variance_epsilon)
+        return h2d, self.mlp(n2)
 
 
 class DecoderModel(nn.Module):
@@ -172,12 +177,13 @@ class CausalLM(nn.Module):
         B, S = input_ids.shape
         cos_sin = self._rope(S, input_ids.device)
         h = ops.embedding(input_ids, self.model.embed_tokens.weight).reshape(B * S, -1)
+        delta = None
         for layer in self.model.layers:
             if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
-                h = checkpoint(layer, h, B, S, cos_sin, use_reentrant=False)
+                h, delta = checkpoint(layer, h, delta, B, S, cos_sin, use_reentrant=False)
             else:
-                h = layer(h, B, S, cos_sin)
-        return self.model.norm(h)
+                h, delta = layer(h, delta, B, S, cos_sin)
+        return ops.add_rmsnorm(h, delta, self.model.norm.weight, self.model.norm.variance_epsilon)[1]
 
     def forward(self, input_ids, attention_mask=None, labels=None, return_logits: bool = False, **_):
         """Causal LM forward.  With ``labels`` the shifted mean token cross-entropy is returned as

@@ -204,6 +204,48 @@ def rmsnorm(x, w, eps: float):
     return ref.rmsnorm(x, w, eps)
 
 
+class _AddRMSNormFn(torch.autograd.Function):
+    """``h = x + delta; y = rmsnorm(h)`` in one kernel; returns ``(h, y)``.  Backward folds the gradient that
+    arrives on ``h`` (the residual path) into the norm's input gradient, which is the gradient of both inputs."""
+
+    @staticmethod
+    def forward(ctx, x, delta, w, eps):
+        ctx.set_materialize_grads(False)      # an unused output arrives as None instead of a zero tensor
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        d2 = delta.reshape(-1, x.shape[-1]).contiguous()
+        h = torch.empty_like(x2)
+        y = torch.empty_like(x2)
+        rstd = torch.empty(x2.shape[0], device=x.device, dtype=torch.float32)
+        _ext.ext().rmsnorm_fwd(x2, w, y, rstd, float(eps), d2, h)
+        _count()
+        ctx.save_for_backward(h, w, rstd)
+        return h.view(x.shape), y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, g_h, g_y):
+        h, w, rstd = ctx.saved_tensors
+        if g_y is None:                       # the normalised output was not used
+            return g_h, g_h, None, None
+        dy2 = g_y.reshape(-1, g_y.shape[-1]).contiguous()
+        res = g_h.reshape(-1, g_h.shape[-1]).contiguous() if g_h is not None else None
+        dx = torch.empty_like(h)
+        dw = torch.zeros(w.numel(), device=w.device, dtype=torch.float32)
+        _ext.ext().rmsnorm_bwd(dy2, h, w, rstd, dx, dw, res)
+        _count(2)
+        dx = dx.view(g_y.shape)
+        return dx, dx, dw.to(w.dtype), None
+
+
+def add_rmsnorm(x, delta, w, eps: float):
+    """Residual update followed by RMSNorm: returns ``(x + delta, rmsnorm(x + delta))``; ``delta=None`` skips the add."""
+    if delta is None:
+        return x, rmsnorm(x, w, eps)
+    if use_kernels(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384 and delta.shape == x.shape:
+        return _AddRMSNormFn.apply(x, delta, w, eps)
+    h = x + delta
+    return h, ref.rmsnorm(h, w, eps)
+
+
 class _HeadNormRopeFn(torch.autograd.Function):
     """Per-head RMSNorm (optional) + RoPE on a ``(tokens, heads*128)`` view."""
 

@@ -253,6 +253,36 @@ def _rope_table(S, theta=1e6, D=128):
     return torch.stack([ang.cos(), ang.sin()], dim=-1).contiguous()  # (S, 64, 2)
 
 
+def test_add_rmsnorm_fwd_bwd():
+    """Fused residual add + RMSNorm: both outputs and the joined gradient against plain PyTorch in fp32."""
+    from himuon_b200 import ops
+
+    torch.manual_seed(5)
+    T, H = 300, 2560
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    d = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16().requires_grad_(True)
+    h, y = ops.add_rmsnorm(x, d, w, 1e-6)
+    gh = torch.randn_like(h)
+    gy = torch.randn_like(y)
+    gx, gd, gw = torch.autograd.grad((h, y), (x, d, w), (gh, gy))
+    xr, dr, wr = x.detach().float().requires_grad_(True), d.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    # value rounded to bf16 like the kernel's h, gradient of the plain sum
+    hr = (xr + dr) + ((xr + dr).bfloat16().float() - (xr + dr)).detach()
+    yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    rgx, rgd, rgw = torch.autograd.grad((hr, yr), (xr, dr, wr), (gh.float(), gy.float()), retain_graph=True)
+    _close(h, hr.detach(), atol=1e-2, rtol=1e-2)
+    _close(y, yr.detach(), atol=3e-2, rtol=2e-2)
+    _close(gx, rgx, atol=5e-2, rtol=3e-2)
+    assert gd.data_ptr() == gx.data_ptr()                    # one gradient tensor serves both inputs
+    _close(gw, rgw, atol=0.5, rtol=3e-2)
+    # only the normalised output used (final norm of the model)
+    h2, y2 = ops.add_rmsnorm(x, d, w, 1e-6)
+    gx2, = torch.autograd.grad(y2, x, gy)
+    rgx2, = torch.autograd.grad(yr, xr, gy.float())
+    _close(gx2, rgx2, atol=5e-2, rtol=3e-2)
+
+
 @pytest.mark.parametrize("use_norm", [True, False])
 def test_headnorm_rope(use_norm):
     e = _ext()
