@@ -76,11 +76,13 @@ static void untile_apply(const at::Tensor& entries, int64_t n_entries, int64_t t
   himuon::untile_apply(reinterpret_cast<const himuon::ApplyEntry*>(entries.data_ptr()), (int)n_entries, (int)total_units,
                        (int)Th, (int)Tw, tiles.data_ptr(), hyper.data_ptr<float>(), param_fp32 ? 1 : 0, cur_stream());
 }
-static void ns_normalize(at::Tensor& tiles, int64_t n_tiles, int64_t tile_elems, double eps) {
+static void ns_normalize(at::Tensor& tiles, int64_t n_tiles, int64_t tile_elems, double eps, const c10::optional<at::Tensor>& out) {
   HM_CHECK(tiles.is_cuda() && is_bf16(tiles) && tiles.is_contiguous(), "ns_normalize: tiles must be contiguous bf16");
   HM_CHECK(tiles.numel() >= n_tiles * tile_elems, "ns_normalize: buffer too small");
+  if (out.has_value())
+    HM_CHECK(out->is_cuda() && is_bf16(*out) && out->is_contiguous() && out->numel() >= n_tiles * tile_elems, "ns_normalize: bad out");
   const c10::cuda::CUDAGuard guard(tiles.device());
-  himuon::ns_normalize(tiles.data_ptr(), n_tiles, tile_elems, (float)eps, cur_stream());
+  himuon::ns_normalize(tiles.data_ptr(), n_tiles, tile_elems, (float)eps, cur_stream(), out.has_value() ? out->data_ptr() : nullptr);
 }
 static void adamw_multi(const at::Tensor& entries, int64_t n_entries, int64_t total_units, const at::Tensor& hyper,
                         at::Tensor& step, int64_t mode, bool param_fp32, bool state_fp32) {
@@ -253,7 +255,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("max_ctas") = 0);
   m.def("momentum_tile", &momentum_tile);
   m.def("untile_apply", &untile_apply);
-  m.def("ns_normalize", &ns_normalize);
+  m.def("ns_normalize", &ns_normalize, py::arg("tiles"), py::arg("n_tiles"), py::arg("tile_elems"), py::arg("eps"),
+        py::arg("out") = py::none());
   m.def("adamw_multi", &adamw_multi);
   m.def("adamw_step_advance", &adamw_step_advance);
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("y"), py::arg("rstd"), py::arg("eps"),

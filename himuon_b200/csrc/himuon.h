@@ -74,7 +74,9 @@ void untile_apply(const ApplyEntry* entries, int n_entries, int total_units, int
                   const float* hyper, int param_fp32, cudaStream_t stream);
 
 // In-place per-tile Frobenius normalisation of a (B, m, n) bf16 buffer: X <- bf16(X / (||X||_F + eps)).
-void ns_normalize(void* tiles_bf16, long long n_tiles, long long tile_elems, float eps, cudaStream_t stream);
+// `out` (same shape, optional): write the normalised tiles there instead of in place.
+void ns_normalize(void* tiles_bf16, long long n_tiles, long long tile_elems, float eps, cudaStream_t stream,
+                  void* out = nullptr);
 
 struct AdamEntry {
   void* param;

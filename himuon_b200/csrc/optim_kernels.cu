@@ -231,10 +231,11 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 __global__ void __launch_bounds__(1024)
-ns_normalize_kernel(__nv_bfloat16* __restrict__ tiles, long long n_tiles, long long tile_elems, float eps) {
+ns_normalize_kernel(const __nv_bfloat16* tiles, __nv_bfloat16* out, long long n_tiles, long long tile_elems, float eps) {
   __shared__ float red[32];
   for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-    __nv_bfloat16* x = tiles + t * tile_elems;
+    const __nv_bfloat16* x = tiles + t * tile_elems;
+    __nv_bfloat16* y = out + t * tile_elems;             // may alias x (in place)
     float ss = 0.f;
     if ((tile_elems & 7) == 0) {
       const long long nv = tile_elems >> 3;
@@ -248,30 +249,32 @@ ns_normalize_kernel(__nv_bfloat16* __restrict__ tiles, long long n_tiles, long l
       for (long long i = threadIdx.x; i < tile_elems; i += blockDim.x) { const float a = __bfloat162float(x[i]); ss += a * a; }
     }
     const float tot = block_sum(ss, red);
-    if (tot == 0.f) continue;  // all-zero (padding) tile stays exactly zero; uniform over the block
-    const float inv = 1.f / (sqrtf(tot) + eps);
+    // an all-zero (padding) tile stays exactly zero (inv = 0 also covers the out-of-place copy); uniform over the block
+    if (tot == 0.f && y == x) continue;
+    const float inv = tot == 0.f ? 0.f : 1.f / (sqrtf(tot) + eps);
     if ((tile_elems & 7) == 0) {
       const long long nv = tile_elems >> 3;
       for (long long i = threadIdx.x; i < nv; i += blockDim.x) {
-        uint4 v = reinterpret_cast<uint4*>(x)[i];
+        uint4 v = reinterpret_cast<const uint4*>(x)[i];
         uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int q = 0; q < 4; ++q) w[q] = pack_bf16x2(bf16_lo(w[q]) * inv, bf16_hi(w[q]) * inv);
         v.x = w[0]; v.y = w[1]; v.z = w[2]; v.w = w[3];
-        reinterpret_cast<uint4*>(x)[i] = v;
+        reinterpret_cast<uint4*>(y)[i] = v;
       }
     } else {
-      for (long long i = threadIdx.x; i < tile_elems; i += blockDim.x) x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) * inv);
+      for (long long i = threadIdx.x; i < tile_elems; i += blockDim.x) y[i] = __float2bfloat16_rn(__bfloat162float(x[i]) * inv);
     }
   }
 }
 
-void ns_normalize(void* tiles, long long n_tiles, long long tile_elems, float eps, cudaStream_t stream) {
+void ns_normalize(void* tiles, long long n_tiles, long long tile_elems, float eps, cudaStream_t stream, void* out) {
   if (n_tiles <= 0) return;
   const long long cap = static_cast<long long>(num_sms()) * 2;
   const int grid = static_cast<int>(n_tiles < cap ? n_tiles : cap);
   const int threads = tile_elems >= 8192 ? 1024 : 256;
-  ns_normalize_kernel<<<grid, threads, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(tiles), n_tiles, tile_elems, eps);
+  ns_normalize_kernel<<<grid, threads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(tiles),
+                                                    reinterpret_cast<__nv_bfloat16*>(out ? out : tiles), n_tiles, tile_elems, eps);
 }
 
 // ------------------------------------------------------------------------------------------------

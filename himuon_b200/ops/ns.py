@@ -69,10 +69,16 @@ def ns_inplace_cuda(X: torch.Tensor, steps: int = 5, eps: float = 1e-7, workspac
         raise ValueError(f"newton_schulz on CUDA needs tile sides that are multiples of 8, got ({m}, {n})")
     ws = workspace or NSWorkspace()
     A, Bm, Y = ws.get(Bt, m, n, X.device)
-    if normalize:
-        e.ns_normalize(X, Bt, m * n, float(eps))
-        _count()
     cur, nxt = X, Y
+    if normalize:
+        # With an odd number of iterations the normalised copy goes to the scratch buffer, so that the ping-pong ends
+        # in X and no copy back is needed.
+        if steps % 2 == 1:
+            e.ns_normalize(X, Bt, m * n, float(eps), Y)
+            cur, nxt = Y, X
+        else:
+            e.ns_normalize(X, Bt, m * n, float(eps))
+        _count()
     wide = m <= n
     for _ in range(steps):
         if wide:
