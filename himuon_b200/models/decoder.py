@@ -51,7 +51,7 @@ class RMSNorm(nn.Module):
         self.variance_epsilon = eps
 
     def forward(self, x):
-        return ops.rmsnorm(x, self.weight, self.variance_epsilon)
+        return ops.rmsnorm(x, self.weight, self.variance_epsilon, defer_dw=True)
 
 
 class Attention(nn.Module):
@@ -80,8 +80,8 @@ class Attention(nn.Module):
             v = self.v_proj(x2d)
         qw = self.q_norm.weight if cfg.qk_norm else None
         kw = self.k_norm.weight if cfg.qk_norm else None
-        q = ops.head_norm_rope(q, qw, cos_sin, Hq, S, D, cfg.rms_norm_eps)
-        k = ops.head_norm_rope(k, kw, cos_sin, Hkv, S, D, cfg.rms_norm_eps)
+        q = ops.head_norm_rope(q, qw, cos_sin, Hq, S, D, cfg.rms_norm_eps, defer_dw=True)
+        k = ops.head_norm_rope(k, kw, cos_sin, Hkv, S, D, cfg.rms_norm_eps, defer_dw=True)
         o = ops.attention(q, k, v, B, S, Hq, Hkv, D)
         return self.o_proj(o)
 
@@ -112,9 +112,10 @@ class DecoderLayer(nn.Module):
         """``delta`` is the previous block's output that has not been added to the residual stream yet (``None``
         for the first layer): every residual add is fused with the RMSNorm that follows it.  Returns the updated
         stream and this layer's own pending MLP output."""
-        h2d, n1 = ops.add_rmsnorm(h2d, delta, self.input_layernorm.weight, self.input_layernorm.variance_epsilon)
+        h2d, n1 = ops.add_rmsnorm(h2d, delta, self.input_layernorm.weight, self.input_layernorm.variance_epsilon, defer_dw=True)
         a = self.self_attn(n1, B, S, cos_sin)
-        h2d, n2 = ops.add_rmsnorm(h2d, a, self.post_attention_layernorm.weight, self.post_attention_layernorm.variance_epsilon)
+        h2d, n2 = ops.add_rmsnorm(h2d, a, self.post_attention_layernorm.weight,
+                                      self.post_attention_layernorm.variance_epsilon, defer_dw=True)
         return h2d, self.mlp(n2)
 
 
@@ -183,7 +184,7 @@ class CausalLM(nn.Module):
                 h, delta = checkpoint(layer, h, delta, B, S, cos_sin, use_reentrant=False)
             else:
                 h, delta = layer(h, delta, B, S, cos_sin)
-        return ops.add_rmsnorm(h, delta, self.model.norm.weight, self.model.norm.variance_epsilon)[1]
+        return ops.add_rmsnorm(h, delta, self.model.norm.weight, self.model.norm.variance_epsilon, defer_dw=True)[1]
 
     def forward(self, input_ids, attention_mask=None, labels=None, return_logits: bool = False, **_):
         """Causal LM forward.  With ``labels`` the shifted mean token cross-entropy is returned as

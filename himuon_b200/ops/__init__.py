@@ -175,10 +175,90 @@ class _SinkLinearRef(torch.autograd.Function):
         return (dy2 @ w).view(x.shape), None, None
 
 
+# ------------------------------------------------------------------------------------------- deferred norm-weight grads
+class _NormGradArena:
+    """fp32 accumulators for the weight gradients of the norm layers.
+
+    The norm backward kernels add their per-column sums straight into a slice of one persistent fp32 buffer; a
+    callback queued on the autograd engine folds all pending slices into the parameters' ``.grad`` once, at the end
+    of the backward pass (one cast, one multi-tensor add, one clear), instead of a zero-fill, a cast and an
+    accumulation kernel per norm call.  Only used for leaf parameters (``defer_dw=True`` from the model code);
+    ``torch.autograd.grad`` callers keep the immediate path.
+    """
+
+    CHUNK = 1 << 20
+
+    def __init__(self, device):
+        self.device = device
+        self.chunks: list[torch.Tensor] = []
+        self.used = self.CHUNK                      # forces the first allocation
+        self.slots: dict[int, tuple] = {}           # id(param) -> (weakref, chunk index, offset, numel)
+        self.pending: dict[int, None] = {}
+        self.queued = False
+
+    def buffer_for(self, w: torch.Tensor) -> torch.Tensor:
+        slot = self.slots.get(id(w))
+        if slot is None or slot[0]() is not w:
+            n = (w.numel() + 3) // 4 * 4            # 16-byte aligned slices (four-wide atomics)
+            if self.used + n > self.CHUNK:
+                self.chunks.append(torch.zeros(max(self.CHUNK, n), device=self.device, dtype=torch.float32))
+                self.used = 0
+            slot = (weakref.ref(w), len(self.chunks) - 1, self.used, w.numel())
+            self.used += n
+            self.slots[id(w)] = slot
+        self.pending[id(w)] = None
+        if not self.queued:
+            self.queued = True
+            torch.autograd.Variable._execution_engine.queue_callback(self.flush)
+        return self.chunks[slot[1]][slot[2]: slot[2] + slot[3]]
+
+    def flush(self) -> None:
+        self.queued = False
+        pending, self.pending = self.pending, {}
+        by_chunk: dict[int, list] = {}
+        for key in pending:
+            ref_w, ci, off, n = self.slots[key]
+            w = ref_w()
+            if w is not None:
+                by_chunk.setdefault(ci, []).append((w, off, n))
+        for ci, items in by_chunk.items():
+            chunk = self.chunks[ci]
+            hi = max(off + n for _, off, n in items)
+            casts: dict[torch.dtype, torch.Tensor] = {}
+            grads, srcs = [], []
+            for w, off, n in items:
+                if w.dtype not in casts:
+                    casts[w.dtype] = chunk[:hi].to(w.dtype)
+                g = casts[w.dtype][off: off + n].view_as(w)
+                if w.grad is None:
+                    w.grad = g.clone()
+                else:
+                    grads.append(w.grad)
+                    srcs.append(g)
+            if grads:
+                torch._foreach_add_(grads, srcs)
+            chunk[:hi].zero_()
+
+
+_NORM_ARENAS: dict = {}
+
+
+def _norm_grad_buffer(w: torch.Tensor) -> torch.Tensor:
+    arena = _NORM_ARENAS.get(w.device)
+    if arena is None:
+        arena = _NORM_ARENAS[w.device] = _NormGradArena(w.device)
+    return arena.buffer_for(w)
+
+
+def _deferrable(w, defer_dw: bool) -> bool:
+    return bool(defer_dw) and w is not None and w.is_leaf and w.requires_grad
+
+
 # ------------------------------------------------------------------------------------------- norms / rope
 class _RMSNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, eps):
+    def forward(ctx, x, w, eps, defer_dw=False):
+        ctx.defer_dw = defer_dw
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         y = torch.empty_like(x2)
         rstd = torch.empty(x2.shape[0], device=x.device, dtype=torch.float32)
@@ -192,15 +272,21 @@ class _RMSNormFn(torch.autograd.Function):
         x2, w, rstd = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
         dx = torch.empty_like(x2)
+        if ctx.defer_dw:
+            _ext.ext().rmsnorm_bwd(dy2, x2, w, rstd, dx, _norm_grad_buffer(w))
+            _count(2)
+            return dx.view(dy.shape), None, None, None
         dw = torch.zeros(w.numel(), device=w.device, dtype=torch.float32)
         _ext.ext().rmsnorm_bwd(dy2, x2, w, rstd, dx, dw)
         _count(2)
-        return dx.view(dy.shape), dw.to(w.dtype), None
+        return dx.view(dy.shape), dw.to(w.dtype), None, None
 
 
-def rmsnorm(x, w, eps: float):
+def rmsnorm(x, w, eps: float, defer_dw: bool = False):
+    """``defer_dw``: accumulate the weight gradient in fp32 and add it to ``w.grad`` once at the end of the backward
+    pass (for leaf parameters trained with ``backward()``; ``torch.autograd.grad`` on ``w`` needs ``False``)."""
     if use_kernels(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384:
-        return _RMSNormFn.apply(x, w, eps)
+        return _RMSNormFn.apply(x, w, eps, _deferrable(w, defer_dw))
     return ref.rmsnorm(x, w, eps)
 
 
@@ -209,7 +295,8 @@ class _AddRMSNormFn(torch.autograd.Function):
     arrives on ``h`` (the residual path) into the norm's input gradient, which is the gradient of both inputs."""
 
     @staticmethod
-    def forward(ctx, x, delta, w, eps):
+    def forward(ctx, x, delta, w, eps, defer_dw=False):
+        ctx.defer_dw = defer_dw
         ctx.set_materialize_grads(False)      # an unused output arrives as None instead of a zero tensor
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         d2 = delta.reshape(-1, x.shape[-1]).contiguous()
@@ -225,23 +312,28 @@ class _AddRMSNormFn(torch.autograd.Function):
     def backward(ctx, g_h, g_y):
         h, w, rstd = ctx.saved_tensors
         if g_y is None:                       # the normalised output was not used
-            return g_h, g_h, None, None
+            return g_h, g_h, None, None, None
         dy2 = g_y.reshape(-1, g_y.shape[-1]).contiguous()
         res = g_h.reshape(-1, g_h.shape[-1]).contiguous() if g_h is not None else None
         dx = torch.empty_like(h)
+        if ctx.defer_dw:
+            _ext.ext().rmsnorm_bwd(dy2, h, w, rstd, dx, _norm_grad_buffer(w), res)
+            _count(2)
+            dx = dx.view(g_y.shape)
+            return dx, dx, None, None, None
         dw = torch.zeros(w.numel(), device=w.device, dtype=torch.float32)
         _ext.ext().rmsnorm_bwd(dy2, h, w, rstd, dx, dw, res)
         _count(2)
         dx = dx.view(g_y.shape)
-        return dx, dx, dw.to(w.dtype), None
+        return dx, dx, dw.to(w.dtype), None, None
 
 
-def add_rmsnorm(x, delta, w, eps: float):
+def add_rmsnorm(x, delta, w, eps: float, defer_dw: bool = False):
     """Residual update followed by RMSNorm: returns ``(x + delta, rmsnorm(x + delta))``; ``delta=None`` skips the add."""
     if delta is None:
-        return x, rmsnorm(x, w, eps)
+        return x, rmsnorm(x, w, eps, defer_dw)
     if use_kernels(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384 and delta.shape == x.shape:
-        return _AddRMSNormFn.apply(x, delta, w, eps)
+        return _AddRMSNormFn.apply(x, delta, w, eps, _deferrable(w, defer_dw))
     h = x + delta
     return h, ref.rmsnorm(h, w, eps)
 
@@ -250,7 +342,8 @@ class _HeadNormRopeFn(torch.autograd.Function):
     """Per-head RMSNorm (optional) + RoPE on a ``(tokens, heads*128)`` view."""
 
     @staticmethod
-    def forward(ctx, x, w, cos_sin, heads, seq_len, eps):
+    def forward(ctx, x, w, cos_sin, heads, seq_len, eps, defer_dw=False):
+        ctx.defer_dw = defer_dw
         y = torch.empty(x.shape[0], heads * 128, device=x.device, dtype=x.dtype)
         rstd = torch.empty(x.shape[0] * heads, device=x.device, dtype=torch.float32) if w is not None else None
         _ext.ext().headnorm_rope_fwd(x, w, y, rstd, cos_sin, heads, seq_len, float(eps))
@@ -265,16 +358,20 @@ class _HeadNormRopeFn(torch.autograd.Function):
         if dy.stride(-1) != 1:
             dy = dy.contiguous()
         dx = torch.empty(dy.shape[0], ctx.heads * 128, device=dy.device, dtype=dy.dtype)
+        if w is not None and ctx.defer_dw:
+            _ext.ext().headnorm_rope_bwd(dy, x, w, rstd, dx, _norm_grad_buffer(w), cos_sin, ctx.heads, ctx.seq_len)
+            _count(2)
+            return dx, None, None, None, None, None, None
         dw = torch.zeros(128, device=dy.device, dtype=torch.float32) if w is not None else None
         _ext.ext().headnorm_rope_bwd(dy, x if w is not None else None, w, rstd, dx, dw, cos_sin, ctx.heads, ctx.seq_len)
         _count(2 if w is not None else 1)
-        return dx, (dw.to(w.dtype) if w is not None else None), None, None, None, None
+        return dx, (dw.to(w.dtype) if w is not None else None), None, None, None, None, None
 
 
-def head_norm_rope(x2d, w, cos_sin, heads: int, seq_len: int, head_dim: int, eps: float):
+def head_norm_rope(x2d, w, cos_sin, heads: int, seq_len: int, head_dim: int, eps: float, defer_dw: bool = False):
     """``x2d``: ``(B*S, heads*head_dim)`` (may be a column slice).  Returns the same layout."""
     if use_kernels(x2d) and head_dim == 128:
-        return _HeadNormRopeFn.apply(x2d, w, cos_sin, heads, seq_len, eps)
+        return _HeadNormRopeFn.apply(x2d, w, cos_sin, heads, seq_len, eps, _deferrable(w, defer_dw))
     T = x2d.shape[0]
     x = x2d.reshape(T // seq_len, seq_len, heads, head_dim)
     if w is not None:
