@@ -126,8 +126,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int item = pair; ok && item < p.total_items; item += n_pairs) {
-        const WorkItem w = decode_item(p, item);
+      WorkCursor cur(p, pair, n_pairs);
+      WorkItem w;
+      while (ok && cur.next(w)) {
         const int tile = w.tile;
         const int b = tile / tiles_per_batch;
         const int r = tile - b * tiles_per_batch;
@@ -165,8 +166,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int item = pair; ok && item < p.total_items; item += n_pairs) {
-        const WorkItem w = decode_item(p, item);
+      WorkCursor cur(p, pair, n_pairs);
+      WorkItem w;
+      while (ok && cur.next(w)) {
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag, p.status, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN2);
@@ -204,8 +206,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint32_t slab_seq = 0;
     const bool issuer = (threadIdx.x == 128);
     if (issuer) tma_prefetch_desc(&tmC);
-    for (int item = pair; item < p.total_items; item += n_pairs) {
-      const WorkItem w = decode_item(p, item);
+    WorkCursor cur(p, pair, n_pairs);
+    WorkItem w;
+    while (cur.next(w)) {
       const int tile = w.tile;
       const int b = tile / tiles_per_batch;
       const int r = tile - b * tiles_per_batch;
@@ -318,6 +321,14 @@ static bool pair_split_enabled() {
   return v;
 }
 
+static bool pair_stream_k_enabled() {
+  static const bool v = [] {
+    const char* e = getenv("HIMUON_GEMM_STREAMK");
+    return !(e && std::string(e) == "0");
+  }();
+  return v;
+}
+
 static bool pair_reduce_out_enabled() {
   static const bool v = [] {
     const char* e = getenv("HIMUON_GEMM_REDUCE_OUT");
@@ -396,7 +407,11 @@ static void launch_gemm2(const GemmArgs& a, cudaStream_t stream) {
   CUtensorMap tmW = tmC;
   const int rem = static_cast<int>(total % cap);
   float* scratch = nullptr;
-  if (pair_split_enabled() && total > cap / 2 && rem > 0 && rem * 2 <= cap && rem <= kPairTailMax && p.kblocks >= 16 &&
+  // Accumulating fp32 outputs need no scratch to split a tile along K (every part just adds into C), so their work is
+  // dealt out in equal contiguous (tile, k-block) ranges whenever whole tiles would not fill the last wave.
+  const bool want_stream = p.reduce_out && pair_stream_k_enabled() && total % cap != 0 && p.kblocks >= 8 &&
+                           total * p.kblocks >= 8LL * cap;
+  if (!want_stream && pair_split_enabled() && total > cap / 2 && rem > 0 && rem * 2 <= cap && rem <= kPairTailMax && p.kblocks >= 16 &&
       (scratch = pair_scratch()) != nullptr) {
     int sl = cap / rem;
     if (sl > p.kblocks / 8) sl = p.kblocks / 8;
@@ -411,7 +426,11 @@ static void launch_gemm2(const GemmArgs& a, cudaStream_t stream) {
       tmW = make_tmap(scratch, 3, dimsW, strW, boxW, 4, true);
     }
   }
-  const long long pairs = p.total_items < cap ? p.total_items : cap;
+  long long pairs = p.total_items < cap ? p.total_items : cap;
+  if (want_stream) {
+    p.stream_k = 1;
+    pairs = cap;
+  }
   kern<<<static_cast<int>(2 * pairs), 256, SMEM, stream>>>(tmA, tmB, tmC, tmW, p);
   if (p.nslices > 1) {
     const long long groups = 256LL * 256 / 4 * rem;

@@ -22,6 +22,8 @@ struct GemmDev {
   // adds the others to its accumulator and runs the epilogue.
   int full_items, total_items, nslices, split_debug;
   int reduce_out;   // pair kernel, fp32 C += alpha*acc (aux == C, beta == 1): whole tiles add into C with TMA reductions
+  int stream_k;     // with reduce_out: every CTA pair takes an equal, contiguous range of (tile, k-block) units and
+                    // adds each partial tile into C, so no wave of tiles is left partly idle
   float* ws;        // one-CTA kernel: [tail tile][slice][BM][BN] fp32; pair kernel: [tail tile][256][256] fp32 running sums
   int* counters;    // arrivals per tail tile (self-resetting)
   int* status;
@@ -43,6 +45,37 @@ __device__ __forceinline__ WorkItem decode_item(const GemmDev& p, int item) {
   }
   return w;
 }
+
+// Walks the work of one CTA (pair): either items first, first+stride, ... of the item list, or (stream_k) the
+// contiguous share [total*first/stride, total*(first+1)/stride) of all (tile, k-block) units, cut at tile boundaries.
+struct WorkCursor {
+  const GemmDev& p;
+  int item, stride;
+  long long u, u1;
+  __device__ __forceinline__ WorkCursor(const GemmDev& p_, int first, int stride_) : p(p_), item(first), stride(stride_), u(0), u1(0) {
+    if (p.stream_k) {
+      const long long total = static_cast<long long>(p.full_items) * p.kblocks;
+      u = total * first / stride_;
+      u1 = total * (first + 1) / stride_;
+    }
+  }
+  __device__ __forceinline__ bool next(WorkItem& w) {
+    if (p.stream_k) {
+      if (u >= u1) return false;
+      const int tile = static_cast<int>(u / p.kblocks);
+      const int kb0 = static_cast<int>(u - static_cast<long long>(tile) * p.kblocks);
+      int len = p.kblocks - kb0;
+      if (len > u1 - u) len = static_cast<int>(u1 - u);
+      w.tile = tile; w.kb0 = kb0; w.kb1 = kb0 + len; w.slice = 0; w.tail = 0; w.split = false;
+      u += len;
+      return true;
+    }
+    if (item >= p.total_items) return false;
+    w = decode_item(p, item);
+    item += stride;
+    return true;
+  }
+};
 
 constexpr int BM = 128;
 constexpr int BK = 64;

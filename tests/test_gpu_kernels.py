@@ -94,6 +94,24 @@ def test_gemm_pair_split_tail(M, N, K):
     _close(acc, ref2, atol=2e-2, rtol=1e-3)
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 2560, 2048), (4096, 2560, 2048), (2560, 9728, 2048), (2304, 2560, 4096)])
+def test_gemm_pair_stream_k_accumulate(M, N, K):
+    """fp32 `C += A^T B` (the weight-gradient GEMM) on shapes whose tile count does not fill the last wave: the work is
+    dealt out as contiguous (tile, k-block) ranges and every partial tile is added into C by TMA reductions."""
+    torch.manual_seed(3)
+    a = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    acc = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    ref = acc.clone()
+    prod = a.float().t() @ b.float()
+    for i in range(2):
+        _ext().gemm(a, b, acc, acc, True, False, 1.0, 1.0, False, 0)
+        ref += prod
+        _close(acc, ref, atol=2e-2, rtol=1e-3)
+    torch.cuda.synchronize()
+    _assert_status_clean()
+
+
 def _ns_ref(x, steps=5):
     a, b, c = 3.4445, -4.7750, 2.0315
     X = x.float()
