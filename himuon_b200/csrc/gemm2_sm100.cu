@@ -224,11 +224,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // K-slice of a last-wave tile: add the fp32 partial into the scratch tile (rows tail*256 + rank*128 ..);
         // a follow-up kernel applies the epilogue to the complete sums
         epilogue_tile_tma<BN2, true>(&tmW, sC, t_acc, row_in_tile, w.tail * 2 * BM + static_cast<int>(rank) * BM, 0, 0, nullptr, 0,
-                                     1 << 30, BN2, 1.f, 0.f, 0, slab_seq, issuer, nullptr, 1, 0, true);
+                                     1 << 30, BN2, 1.f, 0.f, 0, slab_seq, issuer, true);
       } else if (m0 < p.M) {              // uniform: the second CTA of a ragged last row block has nothing to store
         if (p.reduce_out)                 // C += alpha*acc without reading C: the L2 adds the staged slabs
           epilogue_tile_tma<BN2, true>(&tmC, sC, t_acc, row_in_tile, m0, nt * BN2, b, nullptr, 0, p.M, p.N, p.alpha,
-                                       0.f, 0, slab_seq, issuer, nullptr, 1, 0, true);
+                                       0.f, 0, slab_seq, issuer, true);
         else if (p.out_fp32)
           epilogue_tile_tma<BN2, true>(&tmC, sC, t_acc, row_in_tile, m0, nt * BN2, b, p.aux, aux_row, p.M, p.N, p.alpha,
                                        p.beta, p.round_acc, slab_seq, issuer);

@@ -17,15 +17,12 @@ struct GemmDev {
   int round_acc;    // 1: round alpha*acc to bf16 before adding beta*aux
   int tiles_m, tiles_n, kblocks;
   int tma_store;    // 1: epilogue goes through shared-memory slabs and TMA stores (needs 16-byte aligned C rows)
-  // Work list: items [0, full_items) are whole tiles; each tile of the last, mostly empty wave is cut into
-  // `nslices` (2..4) K-ranges, one item each, whose fp32 partial sums meet in `ws`; the slice that arrives last
-  // adds the others to its accumulator and runs the epilogue.
-  int full_items, total_items, nslices, split_debug;
+  // Work list: items [0, full_items) are whole tiles; in the pair kernel each tile of a mostly empty last wave is cut
+  // into `nslices` K-ranges, one item each, whose fp32 partial sums meet in a scratch tile.
+  int full_items, total_items, nslices;
   int reduce_out;   // pair kernel, fp32 C += alpha*acc (aux == C, beta == 1): whole tiles add into C with TMA reductions
   int stream_k;     // with reduce_out: every CTA pair takes an equal, contiguous range of (tile, k-block) units and
                     // adds each partial tile into C, so no wave of tiles is left partly idle
-  float* ws;        // one-CTA kernel: [tail tile][slice][BM][BN] fp32; pair kernel: [tail tile][256][256] fp32 running sums
-  int* counters;    // arrivals per tail tile (self-resetting)
   int* status;
 };
 
@@ -122,8 +119,7 @@ template <int BN, bool OUT_FP32>
 __device__ __forceinline__ void epilogue_tile_tma(const CUtensorMap* tmC, uint8_t* sC, uint32_t t_row, int row_in_tile,
                                                   int m0, int n0, int b, const void* aux, long long aux_row_off,
                                                   int M, int N, float alpha, float beta, int round_acc,
-                                                  uint32_t& slab_seq, bool issuer, const float* partials = nullptr,
-                                                  int nslices = 1, int my_slice = 0, bool reduce_add = false) {
+                                                  uint32_t& slab_seq, bool issuer, bool reduce_add = false) {
   constexpr int SW = OUT_FP32 ? 32 : 64;
   constexpr int SLABS = BN / SW;
   const bool row_ok = (m0 + row_in_tile) < M;
@@ -142,25 +138,6 @@ __device__ __forceinline__ void epilogue_tile_tma(const CUtensorMap* tmC, uint8_
       uint32_t v[32];
       tmem_ld32(t_row + sl * SW + ch * 32, v);
       tmem_ld_wait();
-      if (partials != nullptr) {
-        // split-K tail: add the other slices' partial sums (written by other CTAs, read past L1); all loads of a
-        // slice are issued before they are consumed
-        for (int q = 0; q < nslices; ++q) {
-          if (q == my_slice) continue;
-          const float4* src = reinterpret_cast<const float4*>(
-              partials + (static_cast<long long>(q) * BM + row_in_tile) * BN + sl * SW + ch * 32);
-          float4 t4[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) t4[j] = __ldcg(src + j);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            v[4 * j + 0] = __float_as_uint(__uint_as_float(v[4 * j + 0]) + t4[j].x);
-            v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + t4[j].y);
-            v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + t4[j].z);
-            v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + t4[j].w);
-          }
-        }
-      }
       if (OUT_FP32) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {

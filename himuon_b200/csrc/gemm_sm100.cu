@@ -45,7 +45,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* aux_full = tempty + 2;            // AUX_TMA: one per staging slab
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_full + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* last_flag = abort_flag + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -253,45 +252,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int row_in_tile = ew * 32 + lane;
         const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(acc * BN);
         const long long aux_row = static_cast<long long>(b) * p.strideAux + static_cast<long long>(mt * BM + row_in_tile) * p.ldaux;
-        const float* partials = nullptr;
-        bool run_epilogue = true;
-        if (w.split) {
-          // publish this slice's partial accumulator, then find out whether every other slice has arrived
-          float* tile_ws = p.ws + static_cast<long long>(w.tail) * p.nslices * BM * BN;
-          float* mine = tile_ws + (static_cast<long long>(w.slice) * BM + row_in_tile) * BN;
-#pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 32) {
-            uint32_t v[32];
-            tmem_ld32(t_acc + c0, v);
-            tmem_ld_wait();
-            if (p.split_debug & 1) continue;
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              __stcg(reinterpret_cast<float4*>(mine + c0) + j,
-                     make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
-                                 __uint_as_float(v[4 * j + 3])));
-          }
-          if (!(p.split_debug & 2)) __threadfence();
-          named_barrier(2, 128);
-          if (issuer) {
-            const int old = atomicAdd(p.counters + w.tail, 1);
-            const int last = (old == p.nslices - 1) ? 1 : 0;
-            if (last) p.counters[w.tail] = 0;          // ready for the next launch
-            *last_flag = last;
-          }
-          named_barrier(1, 128);
-          run_epilogue = (*last_flag != 0);
-          if (run_epilogue) { __threadfence(); partials = (p.split_debug & 4) ? nullptr : tile_ws; }
-          named_barrier(2, 128);                       // everyone has read last_flag before it can change again
-        }
-        if (run_epilogue) {
-          if (p.out_fp32)
-            epilogue_tile_tma<BN, true>(&tmC, sC, t_acc, row_in_tile, mt * BM, nt * BN, b, p.aux, aux_row, p.M, p.N,
-                                        p.alpha, p.beta, p.round_acc, slab_seq, issuer, partials, p.nslices, w.slice);
-          else
-            epilogue_tile_tma<BN, false>(&tmC, sC, t_acc, row_in_tile, mt * BM, nt * BN, b, p.aux, aux_row, p.M, p.N,
-                                         p.alpha, p.beta, p.round_acc, slab_seq, issuer, partials, p.nslices, w.slice);
-        }
+        if (p.out_fp32)
+          epilogue_tile_tma<BN, true>(&tmC, sC, t_acc, row_in_tile, mt * BM, nt * BN, b, p.aux, aux_row, p.M, p.N,
+                                      p.alpha, p.beta, p.round_acc, slab_seq, issuer);
+        else
+          epilogue_tile_tma<BN, false>(&tmC, sC, t_acc, row_in_tile, mt * BM, nt * BN, b, p.aux, aux_row, p.M, p.N,
+                                       p.alpha, p.beta, p.round_acc, slab_seq, issuer);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -406,9 +372,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // Developer knobs read once from the environment: HIMUON_GEMM_EPILOGUE=direct, HIMUON_GEMM_BN=128|192|256,
-// HIMUON_GEMM_SPLITK=1 (split the last wave along K; correct but off by default: the single reducing CTA reads the
-// other slices' partial tiles with too little memory parallelism, which costs more than the idle SMs it saves).
-struct GemmTuning { bool force_direct = false; bool no_pair = false; bool no_split = true; int force_bn = 0; int split_debug = 0; int split_max = 4; };
+// HIMUON_GEMM_PAIR=0 (never use the CTA-pair kernel).
+struct GemmTuning { bool force_direct = false; bool no_pair = false; int force_bn = 0; };
 static const GemmTuning& tuning() {
   static GemmTuning t = [] {
     GemmTuning g;
@@ -416,43 +381,11 @@ static const GemmTuning& tuning() {
     if (e && std::string(e) == "direct") g.force_direct = true;
     const char* pr = getenv("HIMUON_GEMM_PAIR");
     if (pr && std::string(pr) == "0") g.no_pair = true;
-    const char* sp = getenv("HIMUON_GEMM_SPLITK");
-    if (sp) g.no_split = std::string(sp) != "1";
-    const char* sd = getenv("HIMUON_GEMM_SPLIT_DEBUG");
-    if (sd) g.split_debug = atoi(sd);
-    const char* sm = getenv("HIMUON_GEMM_SPLIT_MAX");
-    if (sm) g.split_max = atoi(sm);
     const char* b = getenv("HIMUON_GEMM_BN");
     if (b) g.force_bn = atoi(b);
     return g;
   }();
   return t;
-}
-
-// Scratch of the split-K tail: fp32 partial tiles and arrival counters, allocated once per device on first use
-// (well before any stream capture) and shared by every GEMM of the device, which therefore must not overlap each
-// other on different streams when they split.
-constexpr long long kSplitMaxItems = 160;  // slices of one launch (never more than the SM count)
-struct SplitWorkspace { float* ws = nullptr; int* counters = nullptr; };
-static SplitWorkspace& split_workspace() {
-  static SplitWorkspace per_device[64];
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  SplitWorkspace& w = per_device[dev];
-  if (w.ws == nullptr) {
-    void* p1 = nullptr;
-    void* p2 = nullptr;
-    if (cudaMalloc(&p1, kSplitMaxItems * BM * 256 * sizeof(float)) == cudaSuccess &&
-        cudaMemset(p1, 0, kSplitMaxItems * BM * 256 * sizeof(float)) == cudaSuccess &&
-        cudaMalloc(&p2, kSplitMaxItems * sizeof(int)) == cudaSuccess && cudaMemset(p2, 0, kSplitMaxItems * sizeof(int)) == cudaSuccess) {
-      w.ws = static_cast<float*>(p1);
-      w.counters = static_cast<int*>(p2);
-    } else {
-      cudaGetLastError();   // splitting stays off on this device
-    }
-  }
-  return w;
 }
 
 // bf16 output with a bf16 aux tile that TMA can fetch (16-byte aligned base, rows and batches)
@@ -526,26 +459,8 @@ static void launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   }
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batch;
   int sms = a.max_ctas > 0 ? a.max_ctas : num_sms();
-  // Split-K for the last wave when it would leave more than half of the SMs idle.
-  p.full_items = static_cast<int>(total);
+  p.full_items = p.total_items = static_cast<int>(total);
   p.nslices = 1;
-  p.split_debug = tuning().split_debug;
-  p.ws = nullptr;
-  p.counters = nullptr;
-  const int rem = static_cast<int>(total % sms);
-  if (!AUX_TMA && p.tma_store && !tuning().no_split && rem > 0 && rem * 2 <= sms && p.kblocks >= 16) {
-    int sl = sms / rem;
-    if (sl > p.kblocks / 8) sl = p.kblocks / 8;
-    if (sl > tuning().split_max) sl = tuning().split_max;   // the last slice reads (sl - 1) x 128 KB of partials
-    SplitWorkspace& wsp = split_workspace();
-    if (sl >= 2 && wsp.ws != nullptr && static_cast<long long>(rem) * sl <= kSplitMaxItems) {
-      p.nslices = sl;
-      p.full_items = static_cast<int>(total) - rem;
-      p.ws = wsp.ws;
-      p.counters = wsp.counters;
-    }
-  }
-  p.total_items = p.full_items + (p.nslices > 1 ? rem * p.nslices : 0);
   const int grid = static_cast<int>(p.total_items < sms ? p.total_items : sms);
   kern<<<grid, 256, SMEM, stream>>>(tmA, tmB, tmC, tmX, p);
 }
