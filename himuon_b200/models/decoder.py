@@ -74,14 +74,14 @@ class Attention(nn.Module):
         pair = _bank_pair(self.k_proj, self.v_proj)
         if pair is not None:
             kv = pair(x2d)                      # k and v are neighbouring bank slots: one GEMM, column-sliced
-            k, v = kv[:, : Hkv * D], kv[:, Hkv * D:]
+            k, v = ops.split_cols(kv, Hkv * D)
         else:
             k = self.k_proj(x2d)
             v = self.v_proj(x2d)
         qw = self.q_norm.weight if cfg.qk_norm else None
         kw = self.k_norm.weight if cfg.qk_norm else None
-        q = ops.head_norm_rope(q, qw, cos_sin, Hq, S, D, cfg.rms_norm_eps, defer_dw=True)
-        k = ops.head_norm_rope(k, kw, cos_sin, Hkv, S, D, cfg.rms_norm_eps, defer_dw=True)
+        q = ops.head_norm_rope(q, qw, cos_sin, Hq, S, D, cfg.rms_norm_eps, defer_dw=True, inplace_grad=True)
+        k = ops.head_norm_rope(k, kw, cos_sin, Hkv, S, D, cfg.rms_norm_eps, defer_dw=True, inplace_grad=True)
         o = ops.attention(q, k, v, B, S, Hq, Hkv, D)
         return self.o_proj(o)
 

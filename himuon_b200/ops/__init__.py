@@ -342,8 +342,9 @@ class _HeadNormRopeFn(torch.autograd.Function):
     """Per-head RMSNorm (optional) + RoPE on a ``(tokens, heads*128)`` view."""
 
     @staticmethod
-    def forward(ctx, x, w, cos_sin, heads, seq_len, eps, defer_dw=False):
+    def forward(ctx, x, w, cos_sin, heads, seq_len, eps, defer_dw=False, inplace_grad=False):
         ctx.defer_dw = defer_dw
+        ctx.inplace_grad = inplace_grad
         y = torch.empty(x.shape[0], heads * 128, device=x.device, dtype=x.dtype)
         rstd = torch.empty(x.shape[0] * heads, device=x.device, dtype=torch.float32) if w is not None else None
         _ext.ext().headnorm_rope_fwd(x, w, y, rstd, cos_sin, heads, seq_len, float(eps))
@@ -357,26 +358,70 @@ class _HeadNormRopeFn(torch.autograd.Function):
         x, w, rstd, cos_sin = ctx.saved_tensors
         if dy.stride(-1) != 1:
             dy = dy.contiguous()
-        dx = torch.empty(dy.shape[0], ctx.heads * 128, device=dy.device, dtype=dy.dtype)
+        # Each head vector is read completely before it is written, so the input gradient may take the place of the
+        # incoming one (asked for by callers that know dy has no other reader, e.g. a slice of attention's dq|dk|dv).
+        inplace = ctx.inplace_grad and dy.stride(0) % 8 == 0 and dy.data_ptr() % 16 == 0
+        dx = dy if inplace else torch.empty(dy.shape[0], ctx.heads * 128, device=dy.device, dtype=dy.dtype)
         if w is not None and ctx.defer_dw:
             _ext.ext().headnorm_rope_bwd(dy, x, w, rstd, dx, _norm_grad_buffer(w), cos_sin, ctx.heads, ctx.seq_len)
             _count(2)
-            return dx, None, None, None, None, None, None
+            return dx, None, None, None, None, None, None, None
         dw = torch.zeros(128, device=dy.device, dtype=torch.float32) if w is not None else None
         _ext.ext().headnorm_rope_bwd(dy, x if w is not None else None, w, rstd, dx, dw, cos_sin, ctx.heads, ctx.seq_len)
         _count(2 if w is not None else 1)
-        return dx, (dw.to(w.dtype) if w is not None else None), None, None, None, None, None
+        return dx, (dw.to(w.dtype) if w is not None else None), None, None, None, None, None, None
 
 
-def head_norm_rope(x2d, w, cos_sin, heads: int, seq_len: int, head_dim: int, eps: float, defer_dw: bool = False):
-    """``x2d``: ``(B*S, heads*head_dim)`` (may be a column slice).  Returns the same layout."""
+def head_norm_rope(x2d, w, cos_sin, heads: int, seq_len: int, head_dim: int, eps: float, defer_dw: bool = False,
+                   inplace_grad: bool = False):
+    """``x2d``: ``(B*S, heads*head_dim)`` (may be a column slice).  Returns the same layout.  ``inplace_grad``: the
+    backward pass may overwrite the gradient it receives with the gradient it returns."""
     if use_kernels(x2d) and head_dim == 128:
-        return _HeadNormRopeFn.apply(x2d, w, cos_sin, heads, seq_len, eps, _deferrable(w, defer_dw))
+        return _HeadNormRopeFn.apply(x2d, w, cos_sin, heads, seq_len, eps, _deferrable(w, defer_dw), inplace_grad)
     T = x2d.shape[0]
     x = x2d.reshape(T // seq_len, seq_len, heads, head_dim)
     if w is not None:
         x = ref.rmsnorm(x, w, eps)
     return ref.apply_rope(x, cos_sin).reshape(T, heads * head_dim)
+
+
+class _SplitColsFn(torch.autograd.Function):
+    """``x[:, :n0], x[:, n0:]`` whose backward hands the two gradients back as one tensor without a zero fill and an
+    add: when they already are the adjacent column blocks of one buffer (attention's ``dq|dk|dv``) that view is
+    returned as is, otherwise they are copied into a fresh buffer."""
+
+    @staticmethod
+    def forward(ctx, x, n0):
+        ctx.n0 = n0
+        ctx.cols = x.shape[1]
+        return x[:, :n0], x[:, n0:]
+
+    @staticmethod
+    def backward(ctx, g0, g1):
+        n0, n1 = ctx.n0, ctx.cols - ctx.n0
+        if g0 is None and g1 is None:
+            return None, None
+        if (g0 is not None and g1 is not None and g0.stride(1) == 1 and g1.stride(1) == 1
+                and g0.untyped_storage().data_ptr() == g1.untyped_storage().data_ptr()
+                and g0.stride(0) == g1.stride(0) and g1.storage_offset() == g0.storage_offset() + n0
+                and g0.stride(0) >= n0 + n1):
+            return torch.as_strided(g0, (g0.shape[0], n0 + n1), (g0.stride(0), 1), g0.storage_offset()), None
+        ref_t = g0 if g0 is not None else g1
+        out = torch.empty(ref_t.shape[0], n0 + n1, device=ref_t.device, dtype=ref_t.dtype)
+        if g0 is not None:
+            out[:, :n0].copy_(g0)
+        else:
+            out[:, :n0].zero_()
+        if g1 is not None:
+            out[:, n0:].copy_(g1)
+        else:
+            out[:, n0:].zero_()
+        return out, None
+
+
+def split_cols(x2d: torch.Tensor, n0: int):
+    """Column split of a 2-D tensor into ``(x[:, :n0], x[:, n0:])`` with a copy-free backward where possible."""
+    return _SplitColsFn.apply(x2d, n0)
 
 
 # ------------------------------------------------------------------------------------------- attention
