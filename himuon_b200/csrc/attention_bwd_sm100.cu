@@ -187,10 +187,10 @@ flash_bwd_dkv_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           float pr[4], ds[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            float pv = exp2f(fmaf(__uint_as_float(sv[t + u]), p.scale_log2, -lv[u] * kLog2e));
+            float pv = exp2f(fmaf(__uint_as_float(sv[t + u]), p.scale_log2, -lv[u]));
             if (diag && (q0 + c * 32 + t + u < kv_idx)) pv = 0.f;
             pr[u] = pv;
-            ds[u] = pv * (__uint_as_float(dv[t + u]) - dl[u]) * p.scale;
+            ds[u] = pv * (__uint_as_float(dv[t + u]) - dl[u]);      // the softmax scale is applied to dK once, at the end
           }
           pk[t >> 1] = pack_bf16x2(pr[0], pr[1]);
           pk[(t >> 1) + 1] = pack_bf16x2(pr[2], pr[3]);
@@ -212,6 +212,7 @@ flash_bwd_dkv_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       __nv_bfloat16* dst0 = reinterpret_cast<__nv_bfloat16*>(wg == 0 ? p.dv : p.dk) +
                             (static_cast<long long>(b) * p.S + kv_idx) * (wg == 0 ? p.ld_dv : p.ld_dk) + out_head * HD;
       const uint32_t t_src = (wg == 0 ? tDV : tDK) + lane_off;
+      const float out_scale = wg == 0 ? 1.f : p.scale;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
@@ -221,10 +222,10 @@ flash_bwd_dkv_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint4 o4;
-          o4.x = pack_bf16x2(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
-          o4.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
-          o4.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
-          o4.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+          o4.x = pack_bf16x2(__uint_as_float(v[8 * q + 0]) * out_scale, __uint_as_float(v[8 * q + 1]) * out_scale);
+          o4.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]) * out_scale, __uint_as_float(v[8 * q + 3]) * out_scale);
+          o4.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]) * out_scale, __uint_as_float(v[8 * q + 5]) * out_scale);
+          o4.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]) * out_scale, __uint_as_float(v[8 * q + 7]) * out_scale);
           *reinterpret_cast<uint4*>(dst + q * 8) = o4;
         }
       }
@@ -342,7 +343,7 @@ flash_bwd_dq_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int q_idx = qb * AT + row;
     const long long stat_idx = (static_cast<long long>(b) * p.Hq + h) * p.S + q_idx;
-    const float lse2 = p.lse[stat_idx] * kLog2e;
+    const float lse2 = p.lse[stat_idx];
     if (wg == 0) {
       float d = 0.f;
       const __nv_bfloat16* op = reinterpret_cast<const __nv_bfloat16*>(p.o_in) + (static_cast<long long>(b) * p.S + q_idx) * p.ld_o + h * HD;
@@ -379,8 +380,7 @@ flash_bwd_dq_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           float p1 = exp2f(fmaf(__uint_as_float(sv[t + 1]), p.scale_log2, -lse2));
           if (diag && (kv0 + c * 32 + t > q_idx)) p0 = 0.f;
           if (diag && (kv0 + c * 32 + t + 1 > q_idx)) p1 = 0.f;
-          dk[t >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[t]) - delta) * p.scale,
-                                   p1 * (__uint_as_float(dv[t + 1]) - delta) * p.scale);
+          dk[t >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[t]) - delta), p1 * (__uint_as_float(dv[t + 1]) - delta));
         }
         tmem_st16(tDP + buf * BQ + lane_off + c * 16, dk);  // dS over columns of the first dP chunk (already read)
       }
@@ -399,11 +399,11 @@ flash_bwd_dq_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tmem_ld_wait();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          uint4 o4;
-          o4.x = pack_bf16x2(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
-          o4.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
-          o4.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
-          o4.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+          uint4 o4;                                      // dS was left unscaled: the softmax scale lands here
+          o4.x = pack_bf16x2(__uint_as_float(v[8 * q + 0]) * p.scale, __uint_as_float(v[8 * q + 1]) * p.scale);
+          o4.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]) * p.scale, __uint_as_float(v[8 * q + 3]) * p.scale);
+          o4.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]) * p.scale, __uint_as_float(v[8 * q + 5]) * p.scale);
+          o4.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]) * p.scale, __uint_as_float(v[8 * q + 7]) * p.scale);
           *reinterpret_cast<uint4*>(dqp + c * 32 + q * 8) = o4;
         }
       }

@@ -12,7 +12,6 @@ constexpr int HD = 128;                 // head dim
 constexpr uint32_t TILE_BYTES = AT * HD * 2;   // 32 KB: two 64-column halves of 16 KB
 constexpr uint32_t HALF_BYTES = 16384;
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
 
 // Byte offset of the 16-byte chunk `c16` (0..15) of row `r` in a [128 rows][128 cols] bf16 tile
 // stored as two K-major SWIZZLE_128B halves.

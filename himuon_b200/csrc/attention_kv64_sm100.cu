@@ -228,7 +228,7 @@ flash_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
         }
       }
-      if (row_ok) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S + q_idx] = (m_used + log2f(l)) * kLn2;
+      if (row_ok) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S + q_idx] = m_used + log2f(l);   // base-2 log-sum-exp of the scaled scores
     }
   }
   tc_fence_before();
@@ -427,7 +427,7 @@ flash_fwd64_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           }
         }
       }
-      if (row_ok) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S + q_idx] = (m_used + log2f(l)) * kLn2;
+      if (row_ok) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S + q_idx] = m_used + log2f(l);   // base-2 log-sum-exp of the scaled scores
     }
   }
   tc_fence_before();
@@ -525,7 +525,7 @@ flash_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const long long stat_idx = (static_cast<long long>(b) * p.Hq + h) * p.S + q_idx;
     float lse2 = 0.f, delta = 0.f;
     if (row_ok) {
-      lse2 = p.lse[stat_idx] * kLog2e;
+      lse2 = p.lse[stat_idx];
       const __nv_bfloat16* op = reinterpret_cast<const __nv_bfloat16*>(p.o_in) + (static_cast<long long>(b) * p.S + q_idx) * p.ld_o + h * HD;
       const __nv_bfloat16* gp = reinterpret_cast<const __nv_bfloat16*>(p.d_o) + (static_cast<long long>(b) * p.S + q_idx) * p.ld_do + h * HD;
 #pragma unroll 4

@@ -218,7 +218,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
       }
-      if (row_ok) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S + q_idx] = (m_used + log2f(l)) * kLn2;
+      if (row_ok) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S + q_idx] = m_used + log2f(l);   // base-2 log-sum-exp of the scaled scores
     }
   }
   tc_fence_before();
@@ -314,7 +314,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const long long stat_idx = (static_cast<long long>(b) * p.Hq + h) * p.S + q_idx;
     float lse2 = 0.f, delta = 0.f;
     if (row_ok) {
-      lse2 = p.lse[stat_idx] * kLog2e;
+      lse2 = p.lse[stat_idx];
       const __nv_bfloat16* op = reinterpret_cast<const __nv_bfloat16*>(p.o_in) + (static_cast<long long>(b) * p.S + q_idx) * p.ld_o + h * HD;
       const __nv_bfloat16* gp = reinterpret_cast<const __nv_bfloat16*>(p.d_o) + (static_cast<long long>(b) * p.S + q_idx) * p.ld_do + h * HD;
 #pragma unroll 4
@@ -489,7 +489,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       float lse2 = 0.f, delta = 0.f;
       if (row_ok) {
         const long long stat_idx = (static_cast<long long>(b) * p.Hq + h) * p.S + q_idx;
-        lse2 = p.lse[stat_idx] * kLog2e;
+        lse2 = p.lse[stat_idx];
         delta = p.delta[stat_idx];
       }
       if (!mbar_wait(&bars->sp_full, it & 1, abort_flag, p.status, 4)) { ok = false; break; }

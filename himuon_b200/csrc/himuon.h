@@ -131,7 +131,8 @@ void bf16_add_to_f32(const void* src_bf16, float* dst, long long n, cudaStream_t
 
 // ---------------------------------------------------------------- attention (causal GQA, head_dim 128)
 // q: (B, S, Hq, 128), k/v: (B, S, Hkv, 128), o like q; all bf16 with token stride ld_* elements
-// (so q/k/v may be column slices of one fused projection output).  lse: (B, Hq, S) fp32.
+// (so q/k/v may be column slices of one fused projection output).  lse: (B, Hq, S) fp32, the base-2 log-sum-exp of the
+// scaled scores (log2 of the softmax denominator plus the row maximum in base-2 units), as the backward kernels use it.
 struct AttnArgs {
   const void* q; const void* k; const void* v; void* o; float* lse;
   const void* d_o; void* dq; void* dk; void* dv; float* delta;
