@@ -226,9 +226,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         epilogue_tile_tma<BN2, true>(&tmW, sC, t_acc, row_in_tile, w.tail * 2 * BM + static_cast<int>(rank) * BM, 0, 0, nullptr, 0,
                                      1 << 30, BN2, 1.f, 0.f, 0, slab_seq, issuer, true);
       } else if (m0 < p.M) {              // uniform: the second CTA of a ragged last row block has nothing to store
-        if (p.reduce_out)                 // C += alpha*acc without reading C: the L2 adds the staged slabs
+        if (p.reduce_out && p.out_fp32)   // C += alpha*acc without reading C: the L2 adds the staged slabs
           epilogue_tile_tma<BN2, true>(&tmC, sC, t_acc, row_in_tile, m0, nt * BN2, b, nullptr, 0, p.M, p.N, p.alpha,
                                        0.f, 0, slab_seq, issuer, true);
+        else if (p.reduce_out)            // same for a bf16 C: the partial is rounded to bf16, then added in bf16
+          epilogue_tile_tma<BN2, false>(&tmC, sC, t_acc, row_in_tile, m0, nt * BN2, b, nullptr, 0, p.M, p.N, p.alpha,
+                                        0.f, 0, slab_seq, issuer, true);
         else if (p.out_fp32)
           epilogue_tile_tma<BN2, true>(&tmC, sC, t_acc, row_in_tile, m0, nt * BN2, b, p.aux, aux_row, p.M, p.N, p.alpha,
                                        p.beta, p.round_acc, slab_seq, issuer);
@@ -379,7 +382,7 @@ static void launch_gemm2(const GemmArgs& a, cudaStream_t stream) {
   p.kblocks = (a.K + BK - 1) / BK;
   p.tma_store = 1;
   p.nslices = 1;
-  p.reduce_out = (pair_reduce_out_enabled() && a.out_fp32 && a.aux == a.C && a.beta == 1.f && !a.round_acc &&
+  p.reduce_out = (pair_reduce_out_enabled() && a.aux == a.C && a.beta == 1.f && !a.round_acc &&
                   a.ldaux == a.ldc && a.strideAux == a.strideC) ? 1 : 0;
   p.status = status_word_ptr();
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batch;

@@ -20,7 +20,7 @@ struct GemmDev {
   // Work list: items [0, full_items) are whole tiles; in the pair kernel each tile of a mostly empty last wave is cut
   // into `nslices` K-ranges, one item each, whose fp32 partial sums meet in a scratch tile.
   int full_items, total_items, nslices;
-  int reduce_out;   // pair kernel, fp32 C += alpha*acc (aux == C, beta == 1): whole tiles add into C with TMA reductions
+  int reduce_out;   // pair kernel, C += alpha*acc (aux == C, beta == 1; fp32 or bf16): tiles add into C with TMA reductions
   int stream_k;     // with reduce_out: every CTA pair takes an equal, contiguous range of (tile, k-block) units and
                     // adds each partial tile into C, so no wave of tiles is left partly idle
   int* status;

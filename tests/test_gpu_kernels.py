@@ -110,6 +110,15 @@ def test_gemm_pair_stream_k_accumulate(M, N, K):
         _close(acc, ref, atol=2e-2, rtol=1e-3)
     torch.cuda.synchronize()
     _assert_status_clean()
+    # bf16 accumulator (the banks' gradient buffers): every partial is rounded to bf16 and added in bf16
+    acc16 = torch.randn(M, N, device="cuda", dtype=torch.float32).mul_(30).bfloat16()
+    ref16 = acc16.float()
+    for i in range(2):
+        _ext().gemm(a, b, acc16, acc16, True, False, 1.0, 1.0, False, 0)
+        ref16 = (ref16 + prod).bfloat16().float()
+    torch.cuda.synchronize()
+    _assert_status_clean()
+    _close(acc16, ref16, atol=2.0, rtol=2e-2)
 
 
 def _ns_ref(x, steps=5):
