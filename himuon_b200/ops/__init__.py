@@ -88,18 +88,32 @@ class GradSink:
     """
 
     __slots__ = ("buffer", "fresh", "__weakref__")
-    _all: "weakref.WeakSet[GradSink]" = weakref.WeakSet()
+    _log: "list | None" = None          # while a list: every sink written to is appended (CUDA-graph capture)
 
     def __init__(self, buffer: torch.Tensor):
         self.buffer = buffer
         self.fresh = True
-        GradSink._all.add(self)
 
     @classmethod
-    def mark_all_used(cls) -> None:
-        """After a replayed CUDA graph wrote the first micro-batch's gradients (no Python ran): later writes add."""
-        for s in cls._all:
-            s.fresh = False
+    def start_log(cls) -> None:
+        cls._log = []
+
+    @classmethod
+    def stop_log(cls) -> list:
+        """Weak references to the sinks written since ``start_log()``.  A replay of the graph captured meanwhile
+        writes the same sinks without running any Python, so its caller marks them used afterwards."""
+        seen, out = set(), []
+        for s in cls._log or []:
+            if id(s) not in seen:
+                seen.add(id(s))
+                out.append(weakref.ref(s))
+        cls._log = None
+        return out
+
+    def mark_used(self) -> None:
+        self.fresh = False
+        if GradSink._log is not None:
+            GradSink._log.append(self)
 
     def reset(self):
         self.fresh = True
@@ -107,7 +121,7 @@ class GradSink:
     def add_wgrad(self, dy2d: torch.Tensor, x2d: torch.Tensor) -> None:
         gemm(dy2d, x2d, trans_a=True, out=self.buffer, aux=None if self.fresh else self.buffer,
              beta=0.0 if self.fresh else 1.0)
-        self.fresh = False
+        self.mark_used()
 
 
 class _LinearFn(torch.autograd.Function):
@@ -169,7 +183,7 @@ class _SinkLinearRef(torch.autograd.Function):
         dw = (dy2.float().t() @ x2.float()).to(ctx.sink.buffer.dtype)
         if ctx.sink.fresh:
             ctx.sink.buffer.copy_(dw)
-            ctx.sink.fresh = False
+            ctx.sink.mark_used()
         else:
             ctx.sink.buffer.add_(dw)
         return (dy2 @ w).view(x.shape), None, None
@@ -606,7 +620,7 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
                 fresh = False
                 _count(2)
         if need_grad and direct and sink is not None:
-            sink.fresh = False
+            sink.mark_used()
         ctx.direct = direct
         ctx.scale = scale
         if need_grad:

@@ -175,7 +175,7 @@ class Trainer:
         self.graph_microbatch = bool(graph_microbatch) and self.device.type == "cuda"
         self.graph_warmup_steps = int(graph_warmup_steps)
         self._steps_done = 0
-        self._mb_graphs = {}          # first(bool) -> (graph, static loss, launches)
+        self._mb_graphs = {}          # first(bool) -> (graph, static loss, launches, sinks written)
         self._mb_static = None
         self._mb_pool = None
         if self.graph_microbatch:
@@ -207,17 +207,25 @@ class Trainer:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             n0 = ops.launch_count()
-            with torch.cuda.graph(graph, pool=self._mb_pool):
-                loss = self.model(self._mb_static["input_ids"], labels=self._mb_static["labels"]).loss
-                (loss / self.grad_acc).backward()
-                static_loss = loss.detach()
+            ops.GradSink.start_log()
+            try:
+                with torch.cuda.graph(graph, pool=self._mb_pool):
+                    loss = self.model(self._mb_static["input_ids"], labels=self._mb_static["labels"]).loss
+                    (loss / self.grad_acc).backward()
+                    static_loss = loss.detach()
+            finally:
+                written = ops.GradSink.stop_log()
             self._mb_pool = graph.pool()
-            entry = (graph, static_loss, ops.launch_count() - n0)     # the capture ran the wrappers once: counted
+            # the capture ran the wrappers once (launches counted); it also tells which gradient sinks a replay writes
+            entry = (graph, static_loss, ops.launch_count() - n0, written)
             self._mb_graphs[first] = entry
         else:
             ops.add_launches(entry[2])
         entry[0].replay()
-        ops.GradSink.mark_all_used()
+        for ref_sink in entry[3]:
+            sink = ref_sink()
+            if sink is not None:
+                sink.fresh = False
         return entry[1].clone()
 
     def _to_device(self, batch):
