@@ -69,7 +69,7 @@ def test_gemm_batched_epilogue_and_fp32_accumulate():
     _close(acc, ref2, atol=1e-2, rtol=1e-3)
 
 
-@pytest.mark.parametrize("M,N,K", [(2048, 2560, 2560), (2000, 2560, 9728), (2560, 2304, 2048)])
+@pytest.mark.parametrize("M,N,K", [(2048, 2560, 2560), (2000, 2560, 9728), (2560, 2304, 2048), (11520, 2560, 4096)])
 def test_gemm_pair_split_tail(M, N, K):
     """Shapes whose last wave of 256x256 tiles is mostly idle: the tail tiles are cut along K, summed in an fp32
     scratch by TMA reductions and finished by a second kernel.  Run twice (the scratch must come back zeroed), with
@@ -94,7 +94,8 @@ def test_gemm_pair_split_tail(M, N, K):
     _close(acc, ref2, atol=2e-2, rtol=1e-3)
 
 
-@pytest.mark.parametrize("M,N,K", [(2048, 2560, 2048), (4096, 2560, 2048), (2560, 9728, 2048), (2304, 2560, 4096)])
+@pytest.mark.parametrize("M,N,K", [(2048, 2560, 2048), (4096, 2560, 2048), (2560, 9728, 2048), (2304, 2560, 4096),
+                                   (19456, 2560, 2048)])
 def test_gemm_pair_stream_k_accumulate(M, N, K):
     """fp32 `C += A^T B` (the weight-gradient GEMM) on shapes whose tile count does not fill the last wave: the work is
     dealt out as contiguous (tile, k-block) ranges and every partial tile is added into C by TMA reductions."""
