@@ -280,6 +280,26 @@ void ns_normalize(void* tiles, long long n_tiles, long long tile_elems, float ep
 // ------------------------------------------------------------------------------------------------
 constexpr int kAdamUnit = 4096;  // elements per work unit
 
+// The three parameter-update conventions (0: HiMuon's fallback, 1: Muon / MuonFsdp, 2: plain AdamW, decay after the step).
+__device__ __forceinline__ float adam_apply(int mode, float pi, float mi, float vi, float lr, float wd, float eps,
+                                            float bc1, float bc2) {
+  if (mode == 0) {
+    const float u = (mi / bc1) / (sqrtf(vi) / sqrtf(bc2) + eps);
+    if (wd > 0.f) pi *= 1.f - lr * wd;
+    pi -= lr * u;
+  } else if (mode == 1) {
+    const float u = mi / (eps + sqrtf(vi));
+    const float scale = bc1 / sqrtf(bc2);
+    if (wd > 0.f) pi *= 1.f - lr * wd;
+    pi -= (lr / scale) * u;
+  } else {
+    const float u = mi / (sqrtf(vi) + eps);
+    pi -= lr * sqrtf(bc2) / bc1 * u;
+    if (wd > 0.f) pi -= lr * wd * pi;
+  }
+  return pi;
+}
+
 template <typename P, typename S>
 __global__ void __launch_bounds__(256)
 adamw_multi_kernel(const AdamEntry* __restrict__ entries, int n_entries, long long total_units,
@@ -301,7 +321,45 @@ adamw_multi_kernel(const AdamEntry* __restrict__ entries, int n_entries, long lo
     const S* g = reinterpret_cast<const S*>(e.grad);
     S* m = reinterpret_cast<S*>(e.m);
     S* v = reinterpret_cast<S*>(e.v);
-    for (long long i = base + threadIdx.x; i < end; i += blockDim.x) {
+    long long scalar_from = base;
+    if (sizeof(P) == 2 && sizeof(S) == 2 &&
+        ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
+          reinterpret_cast<uintptr_t>(v)) & 15) == 0) {
+      // all-bf16 tensors: eight elements per thread and access (units start on multiples of 4096 elements)
+      const long long nvec = (end - base) >> 3;
+      for (long long k = threadIdx.x; k < nvec; k += blockDim.x) {
+        const long long i = base + (k << 3);
+        const uint4 g4 = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(e.grad) + i);
+        uint4 m4 = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(e.m) + i);
+        uint4 v4 = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(e.v) + i);
+        uint4 p4 = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(e.param) + i);
+        const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+        uint32_t mw[4] = {m4.x, m4.y, m4.z, m4.w}, vw[4] = {v4.x, v4.y, v4.z, v4.w}, pw[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float mo[2], vo[2], po[2];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const float gi = hh ? bf16_hi(gw[q]) : bf16_lo(gw[q]);
+            float mi = hh ? bf16_hi(mw[q]) : bf16_lo(mw[q]);
+            float vi = hh ? bf16_hi(vw[q]) : bf16_lo(vw[q]);
+            float pi = hh ? bf16_hi(pw[q]) : bf16_lo(pw[q]);
+            mi = round_bf16(mi + (gi - mi) * (1.f - b1));
+            vi = round_bf16(vi + (gi * gi - vi) * (1.f - b2));
+            pi = adam_apply(mode, pi, mi, vi, lr, wd, eps, bc1, bc2);
+            mo[hh] = mi; vo[hh] = vi; po[hh] = pi;
+          }
+          mw[q] = pack_bf16x2(mo[0], mo[1]);
+          vw[q] = pack_bf16x2(vo[0], vo[1]);
+          pw[q] = pack_bf16x2(po[0], po[1]);
+        }
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(e.m) + i) = make_uint4(mw[0], mw[1], mw[2], mw[3]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(e.v) + i) = make_uint4(vw[0], vw[1], vw[2], vw[3]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(e.param) + i) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+      }
+      scalar_from = base + (nvec << 3);
+    }
+    for (long long i = scalar_from + threadIdx.x; i < end; i += blockDim.x) {
       const float gi = ldf(g + i);
       float mi = ldf(m + i), vi = ldf(v + i);
       mi = mi + (gi - mi) * (1.f - b1);
@@ -309,22 +367,7 @@ adamw_multi_kernel(const AdamEntry* __restrict__ entries, int n_entries, long lo
       if (sizeof(S) == 2) { mi = round_bf16(mi); vi = round_bf16(vi); }
       stf(m + i, mi);
       stf(v + i, vi);
-      float pi = ldf(p + i);
-      if (mode == 0) {
-        const float u = (mi / bc1) / (sqrtf(vi) / sqrtf(bc2) + eps);
-        if (wd > 0.f) pi *= 1.f - lr * wd;
-        pi -= lr * u;
-      } else if (mode == 1) {
-        const float u = mi / (eps + sqrtf(vi));
-        const float scale = bc1 / sqrtf(bc2);
-        if (wd > 0.f) pi *= 1.f - lr * wd;
-        pi -= (lr / scale) * u;
-      } else {
-        const float u = mi / (sqrtf(vi) + eps);
-        pi -= lr * sqrtf(bc2) / bc1 * u;
-        if (wd > 0.f) pi -= lr * wd * pi;
-      }
-      stf(p + i, pi);
+      stf(p + i, adam_apply(mode, ldf(p + i), mi, vi, lr, wd, eps, bc1, bc2));
     }
   }
 }
