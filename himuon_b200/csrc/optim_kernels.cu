@@ -57,41 +57,63 @@ momentum_tile_kernel(const MomTileEntry* __restrict__ entries, int n_entries, in
     if (vec) {
       const int vec_per_row = Tw / 8;
       const int nvec = (i1 - i0) * vec_per_row;
-      for (int x = threadIdx.x; x < nvec; x += blockDim.x) {
-        const int i = i0 + x / vec_per_row;
-        const int j = (x % vec_per_row) * 8;
-        const int gi = tr * Th + i, gj = tc * Tw + j;
-        uint4 o = make_uint4(0, 0, 0, 0);
-        if (gi < e.h && gj < e.w) {
-          const long long off = static_cast<long long>(gi) * e.ld + gj;
-          float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-          for (int s = 0; s < n_src; ++s) {
-            const uint4 gv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(e.grad[s]) + off);
-            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+      // two vectors per thread and pass, their loads issued together
+      for (int x0 = threadIdx.x; x0 < nvec; x0 += 2 * blockDim.x) {
+        int xs[2] = {x0, x0 + static_cast<int>(blockDim.x)};
+        bool live[2], inside[2];
+        int ii[2], jj[2];
+        long long off[2], moff[2];
+        float g[2][8];
+        uint4 mv[2];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) { g[2 * q] += bf16_lo(gw[q]); g[2 * q + 1] += bf16_hi(gw[q]); }
-          }
-          const long long moff = static_cast<long long>(gi) * e.w + gj;
-          uint4 mv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(mom) + moff);
-          const uint32_t mw[4] = {mv.x, mv.y, mv.z, mv.w};
-          float r[8], m[8];
+        for (int u = 0; u < 2; ++u) {
+          live[u] = xs[u] < nvec;
+          ii[u] = i0 + xs[u] / vec_per_row;
+          jj[u] = (xs[u] % vec_per_row) * 8;
+          const int gi = tr * Th + ii[u], gj = tc * Tw + jj[u];
+          inside[u] = live[u] && gi < e.h && gj < e.w;
+          off[u] = static_cast<long long>(gi) * e.ld + gj;
+          moff[u] = static_cast<long long>(gi) * e.w + gj;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) { m[2 * q] = bf16_lo(mw[q]); m[2 * q + 1] = bf16_hi(mw[q]); }
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            // the gradient as the optimizer would see it (stored precision), then buf = mu*buf + g
-            const float gq = round_bf16(g[q] * gscale);
-            const float b = round_bf16(round_bf16(m[q] * mu) + gq);
-            m[q] = b;
-            r[q] = nesterov ? round_bf16(gq + mu * b) : b;
-          }
-          mv.x = pack_bf16x2(m[0], m[1]); mv.y = pack_bf16x2(m[2], m[3]);
-          mv.z = pack_bf16x2(m[4], m[5]); mv.w = pack_bf16x2(m[6], m[7]);
-          *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(mom) + moff) = mv;
-          o.x = pack_bf16x2(r[0], r[1]); o.y = pack_bf16x2(r[2], r[3]);
-          o.z = pack_bf16x2(r[4], r[5]); o.w = pack_bf16x2(r[6], r[7]);
+          for (int q = 0; q < 8; ++q) g[u][q] = 0.f;
+          mv[u] = make_uint4(0, 0, 0, 0);
+          if (inside[u]) mv[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(mom) + moff[u]);
         }
-        *reinterpret_cast<uint4*>(out + static_cast<long long>(i) * Tw + j) = o;
+        for (int sidx = 0; sidx < n_src; ++sidx) {
+          uint4 gv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+#pragma unroll
+          for (int u = 0; u < 2; ++u)
+            if (inside[u]) gv[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(e.grad[sidx]) + off[u]);
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const uint32_t gw[4] = {gv[u].x, gv[u].y, gv[u].z, gv[u].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { g[u][2 * q] += bf16_lo(gw[q]); g[u][2 * q + 1] += bf16_hi(gw[q]); }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (!live[u]) continue;
+          uint4 o = make_uint4(0, 0, 0, 0);
+          if (inside[u]) {
+            const uint32_t mw[4] = {mv[u].x, mv[u].y, mv[u].z, mv[u].w};
+            float r[8], m[8];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { m[2 * q] = bf16_lo(mw[q]); m[2 * q + 1] = bf16_hi(mw[q]); }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              // the gradient as the optimizer would see it (stored precision), then buf = mu*buf + g
+              const float gq = round_bf16(g[u][q] * gscale);
+              const float bq = round_bf16(round_bf16(m[q] * mu) + gq);
+              m[q] = bq;
+              r[q] = nesterov ? round_bf16(gq + mu * bq) : bq;
+            }
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(mom) + moff[u]) =
+                make_uint4(pack_bf16x2(m[0], m[1]), pack_bf16x2(m[2], m[3]), pack_bf16x2(m[4], m[5]), pack_bf16x2(m[6], m[7]));
+            o = make_uint4(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]), pack_bf16x2(r[4], r[5]), pack_bf16x2(r[6], r[7]));
+          }
+          *reinterpret_cast<uint4*>(out + static_cast<long long>(ii[u]) * Tw + jj[u]) = o;
+        }
       }
     } else {
       const int n = (i1 - i0) * Tw;
@@ -239,8 +261,21 @@ ns_normalize_kernel(const __nv_bfloat16* tiles, __nv_bfloat16* out, long long n_
     float ss = 0.f;
     if ((tile_elems & 7) == 0) {
       const long long nv = tile_elems >> 3;
-      for (long long i = threadIdx.x; i < nv; i += blockDim.x) {
-        const uint4 v = reinterpret_cast<const uint4*>(x)[i];
+      const uint4* xv = reinterpret_cast<const uint4*>(x);
+      long long i = threadIdx.x;
+      for (; i + 3 * blockDim.x < nv; i += 4 * blockDim.x) {      // four independent loads in flight per thread
+        uint4 v4[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v4[u] = xv[i + u * blockDim.x];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t w[4] = {v4[u].x, v4[u].y, v4[u].z, v4[u].w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) { const float a = bf16_lo(w[q]), b = bf16_hi(w[q]); ss += a * a + b * b; }
+        }
+      }
+      for (; i < nv; i += blockDim.x) {
+        const uint4 v = xv[i];
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int q = 0; q < 4; ++q) { const float a = bf16_lo(w[q]), b = bf16_hi(w[q]); ss += a * a + b * b; }
@@ -254,13 +289,27 @@ ns_normalize_kernel(const __nv_bfloat16* tiles, __nv_bfloat16* out, long long n_
     const float inv = tot == 0.f ? 0.f : 1.f / (sqrtf(tot) + eps);
     if ((tile_elems & 7) == 0) {
       const long long nv = tile_elems >> 3;
-      for (long long i = threadIdx.x; i < nv; i += blockDim.x) {
-        uint4 v = reinterpret_cast<const uint4*>(x)[i];
+      const uint4* xv = reinterpret_cast<const uint4*>(x);
+      uint4* yv = reinterpret_cast<uint4*>(y);
+      long long i = threadIdx.x;
+      for (; i + 3 * blockDim.x < nv; i += 4 * blockDim.x) {
+        uint4 v4[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v4[u] = xv[i + u * blockDim.x];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint32_t w[4] = {v4[u].x, v4[u].y, v4[u].z, v4[u].w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) w[q] = pack_bf16x2(bf16_lo(w[q]) * inv, bf16_hi(w[q]) * inv);
+          yv[i + u * blockDim.x] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      for (; i < nv; i += blockDim.x) {
+        uint4 v = xv[i];
         uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int q = 0; q < 4; ++q) w[q] = pack_bf16x2(bf16_lo(w[q]) * inv, bf16_hi(w[q]) * inv);
-        v.x = w[0]; v.y = w[1]; v.z = w[2]; v.w = w[3];
-        reinterpret_cast<uint4*>(y)[i] = v;
+        yv[i] = make_uint4(w[0], w[1], w[2], w[3]);
       }
     } else {
       for (long long i = threadIdx.x; i < tile_elems; i += blockDim.x) y[i] = __float2bfloat16_rn(__bfloat162float(x[i]) * inv);
