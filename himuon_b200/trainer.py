@@ -350,6 +350,8 @@ def run_training(args, mode: str) -> dict:
     trainer = Trainer(model, optimizer, scheduler, engine, args.gradient_accumulation_steps, device,
                       graph_microbatch=bool(getattr(args, "cuda_graph_step", False)))
     trainer.zero_set_to_none = not args.cuda_graph if hasattr(optimizer, "reconfigure") else True
+    if trainer.graph_microbatch:
+        trainer.zero_set_to_none = False       # captured graphs write into the gradient tensors that exist at capture
     budget = TimeBudget(args.time_budget)
     eos = getattr(tokenizer, "eos_token_id", None)
     global_step, tokens_seen, micro = 0, 0, []
