@@ -273,6 +273,8 @@ class _RMSNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, eps, defer_dw=False):
         ctx.defer_dw = defer_dw
+        # the parameter object itself: under activation checkpointing saved_tensors hands back a detached copy
+        ctx.w_param = w if defer_dw else None
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         y = torch.empty_like(x2)
         rstd = torch.empty(x2.shape[0], device=x.device, dtype=torch.float32)
@@ -287,7 +289,7 @@ class _RMSNormFn(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
         dx = torch.empty_like(x2)
         if ctx.defer_dw:
-            _ext.ext().rmsnorm_bwd(dy2, x2, w, rstd, dx, _norm_grad_buffer(w))
+            _ext.ext().rmsnorm_bwd(dy2, x2, w, rstd, dx, _norm_grad_buffer(ctx.w_param))
             _count(2)
             return dx.view(dy.shape), None, None, None
         dw = torch.zeros(w.numel(), device=w.device, dtype=torch.float32)
@@ -311,6 +313,8 @@ class _AddRMSNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, delta, w, eps, defer_dw=False):
         ctx.defer_dw = defer_dw
+        # the parameter object itself: under activation checkpointing saved_tensors hands back a detached copy
+        ctx.w_param = w if defer_dw else None
         ctx.set_materialize_grads(False)      # an unused output arrives as None instead of a zero tensor
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         d2 = delta.reshape(-1, x.shape[-1]).contiguous()
@@ -331,7 +335,7 @@ class _AddRMSNormFn(torch.autograd.Function):
         res = g_h.reshape(-1, g_h.shape[-1]).contiguous() if g_h is not None else None
         dx = torch.empty_like(h)
         if ctx.defer_dw:
-            _ext.ext().rmsnorm_bwd(dy2, h, w, rstd, dx, _norm_grad_buffer(w), res)
+            _ext.ext().rmsnorm_bwd(dy2, h, w, rstd, dx, _norm_grad_buffer(ctx.w_param), res)
             _count(2)
             dx = dx.view(g_y.shape)
             return dx, dx, None, None, None
@@ -358,6 +362,8 @@ class _HeadNormRopeFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, cos_sin, heads, seq_len, eps, defer_dw=False, inplace_grad=False):
         ctx.defer_dw = defer_dw
+        # the parameter object itself: under activation checkpointing saved_tensors hands back a detached copy
+        ctx.w_param = w if defer_dw else None
         ctx.inplace_grad = inplace_grad
         y = torch.empty(x.shape[0], heads * 128, device=x.device, dtype=x.dtype)
         rstd = torch.empty(x.shape[0] * heads, device=x.device, dtype=torch.float32) if w is not None else None
@@ -377,7 +383,7 @@ class _HeadNormRopeFn(torch.autograd.Function):
         inplace = ctx.inplace_grad and dy.stride(0) % 8 == 0 and dy.data_ptr() % 16 == 0
         dx = dy if inplace else torch.empty(dy.shape[0], ctx.heads * 128, device=dy.device, dtype=dy.dtype)
         if w is not None and ctx.defer_dw:
-            _ext.ext().headnorm_rope_bwd(dy, x, w, rstd, dx, _norm_grad_buffer(w), cos_sin, ctx.heads, ctx.seq_len)
+            _ext.ext().headnorm_rope_bwd(dy, x, w, rstd, dx, _norm_grad_buffer(ctx.w_param), cos_sin, ctx.heads, ctx.seq_len)
             _count(2)
             return dx, None, None, None, None, None, None, None
         dw = torch.zeros(128, device=dy.device, dtype=torch.float32) if w is not None else None

@@ -123,3 +123,24 @@ def test_trainer_microbatch_graph_matches_eager():
         c = _cos(p_eager[n], p_graph[n]).item()
         assert c > 0.999, (n, c)
     ops.check_status()
+
+
+def test_gradient_checkpointing_gives_the_same_gradients_on_the_kernel_path():
+    """Per-layer activation checkpointing (the CLI default of train_ddp.py / train_fsdp.py) recomputes each layer in
+    backward: loss and every gradient, including the deferred norm-weight gradients, must match the plain run."""
+    from himuon_b200.models import CausalLM
+
+    torch.manual_seed(0)
+    plain = CausalLM(_small_cfg("qwen3")).cuda().bfloat16()
+    ckpt = copy.deepcopy(plain)
+    ckpt.gradient_checkpointing_enable()
+    ids = torch.randint(0, 2048, (2, 256), device="cuda")
+    for m in (plain, ckpt):
+        m.train()
+        for _ in range(2):                                   # two accumulation micro-steps
+            m(ids, labels=ids).loss.backward()
+    torch.cuda.synchronize()
+    for (n, a), (_, b) in zip(plain.named_parameters(), ckpt.named_parameters()):
+        assert a.grad is not None and b.grad is not None, n
+        c = _cos(a.grad, b.grad).item()
+        assert c > 0.9999, (n, c)

@@ -105,3 +105,26 @@ def test_trainer_graph_switch_falls_back_to_eager_on_cpu():
     losses = [tr.read_loss(tr.train_step([{"input_ids": ids, "labels": ids}] * 2)) for _ in range(5)]
     assert losses[-1] < losses[0]
     assert tr._mb_graphs == {} and tr.d2h_bytes == 5 * 4
+
+
+def test_gradient_checkpointing_matches_plain_backward_on_the_fallback_path():
+    from himuon_b200.models import CausalLM, DecoderConfig
+
+    torch.manual_seed(0)
+    cfg = DecoderConfig(model_type="qwen3", vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=3,
+                        num_attention_heads=2, num_key_value_heads=1, head_dim=16, rms_norm_eps=1e-6, rope_theta=1e4,
+                        tie_word_embeddings=True, max_position_embeddings=64)
+    plain = CausalLM(cfg)
+    import copy
+    ckpt = copy.deepcopy(plain)
+    ckpt.gradient_checkpointing_enable()
+    ids = torch.randint(0, 64, (2, 16))
+    losses = []
+    for m in (plain, ckpt):
+        m.train()
+        loss = m(ids, labels=ids).loss
+        loss.backward()
+        losses.append(loss.item())
+    assert abs(losses[0] - losses[1]) < 1e-6
+    for (n, a), (_, b) in zip(plain.named_parameters(), ckpt.named_parameters()):
+        assert torch.allclose(a.grad, b.grad, atol=1e-6), n
