@@ -133,3 +133,30 @@ def test_muon_full_matrix_step_and_fallback():
     expect = p0 * (1 - 0.01 * 0.1) - 0.01 * 0.2 * math.sqrt(40) * u
     assert torch.allclose(p, expect, atol=1e-6)
     assert (bias < 0).all()
+
+
+def test_dispatch_plan_accounts_for_every_tile_in_each_split_regime():
+    """Counterpart of the reference's dispatch tests (tests/integration/test_himuon_dispatch.py): the bucket plan
+    holds every tile of every parameter exactly once and cuts a bucket into balanced chunks below, at and above the
+    per-call cap."""
+    shapes = [(64, 96), (64, 96), (40, 70), (128, 32)]
+    tile = 32
+    expected = [math.ceil(h / tile) * math.ceil(w / tile) for h, w in shapes]      # 6, 6, 6, 4
+    total = sum(expected)
+    for b_hw in (total + 5, total, total - 1, 7, 1):
+        model = make_linear_model(shapes)
+        opt = HiMuon(model.parameters(), tile_size=tile, b_hw=b_hw, cuda_graph=False)
+        seed_grads(model)
+        opt.step()
+        plan = opt.xlayer_plan()
+        assert len(plan) == 1
+        b = plan[0]
+        by_id = {id(p): tuple(p.shape) for p in model.parameters()}
+        counts = {by_id[i]: [] for i in b["param_ids"]}
+        for i, c in zip(b["param_ids"], b["tile_count_per_param"]):
+            counts[by_id[i]].append(c)
+        assert sorted(c for v in counts.values() for c in v) == sorted(expected)
+        assert b["B_total"] == total and b["B_hw"] == b_hw
+        assert sum(b["chunk_sizes"]) == total and max(b["chunk_sizes"]) <= b_hw
+        assert b["n_calls"] == len(b["chunk_sizes"]) == math.ceil(total / b_hw)
+        assert max(b["chunk_sizes"]) - min(b["chunk_sizes"]) <= 1                   # balanced, no tiny last chunk
