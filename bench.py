@@ -49,6 +49,8 @@ def parse():
     p.add_argument("--grad-acc", type=int, default=GRAD_ACC)
     p.add_argument("--tile", type=int, default=TILE)
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--peer-weights", action="store_true",
+                   help="no gathered copy of the banks: the GEMMs read weight tiles from the owner rank over NVLink")
     p.add_argument("--no-step-graph", action="store_true",
                    help="run forward/backward eagerly instead of replaying the captured micro-batch CUDA graphs")
     p.add_argument("--engine", type=str, default="fsdp", choices=["fsdp", "ddp"],
@@ -129,7 +131,7 @@ def run_ours(args):
     with torch.device(device):
         model = CausalLM(cfg).to(torch.bfloat16)
     if args.engine == "fsdp":
-        engine = ShardedEngine(model, use_banks=args.optimizer in ("himuon", "muon-fsdp"))
+        engine = ShardedEngine(model, use_banks=args.optimizer in ("himuon", "muon-fsdp"), peer_weights=args.peer_weights)
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
         engine = DataParallelEngine(model)
@@ -199,7 +201,7 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model, "global_batch": args.micro_batch * args.grad_acc * world,
                        "seq_len": args.seq_len, "micro_batch_per_gpu": args.micro_batch, "grad_acc": args.grad_acc,
-                       "parallelism": f"fsdp-banks{world}" if args.engine == "fsdp" else f"dp{world}",
+                       "parallelism": (f"fsdp-banks{world}" + ("-peer-weights" if args.peer_weights else "")) if args.engine == "fsdp" else f"dp{world}",
                        "optimizer": f"{args.optimizer} tile {args.tile}, lr {ns.lr}, wd {WD}, cuda graph",
                        "forward_backward": "eager" if args.no_step_graph else "micro-batch CUDA graphs (public Trainer option)",
                        "activation_checkpointing": False,

@@ -36,12 +36,16 @@ from .symm import SymmetricHeap, _world
 
 class _BankState:
     __slots__ = ("spec", "n_local", "shard", "shard_off", "grad_full", "grad_off", "gathered", "param", "sinks",
-                 "pair_sinks")
+                 "pair_sinks", "peer_shards")
 
 
 class ShardedEngine:
     def __init__(self, model: nn.Module, use_banks: bool = True, cpu_offload: bool = False, timeout_s: float = 120.0,
-                 gather_blocks: int = 0):
+                 gather_blocks: int = 0, peer_weights: bool = False):
+        """``peer_weights``: keep no gathered copy of the banks; every projection's GEMM (forward and dgrad) reads
+        the weight tiles by TMA straight from the owner rank's shard over NVLink, so the all-gather is fused into the
+        GEMMs' operand loads.  Saves one full copy of the banks and the per-step re-gather at the price of fetching
+        the weights over NVLink in every micro-step; off by default (180 GB of HBM hold the copy)."""
         self.model = model
         self.rank, self.world = _world()
         self.cpu_offload = cpu_offload
@@ -49,6 +53,7 @@ class ShardedEngine:
         first = next(model.parameters())
         self.device, self.dtype = first.device, first.dtype
         self.cuda = self.device.type == "cuda"
+        self.peer_weights = bool(peer_weights) and self.cuda and self.dtype == torch.bfloat16
         esz = torch.empty((), dtype=self.dtype).element_size()
         self.banks = None
         bank_full = []
@@ -97,8 +102,14 @@ class ShardedEngine:
             st.shard.copy_(full.data[self.rank * st.n_local:(self.rank + 1) * st.n_local])
             st.grad_full, st.grad_off = self.heap.alloc((n_pad, H, W), self.dtype)
             st.grad_full.zero_()
+            st.peer_shards = None
             if self.world == 1:
                 st.gathered = st.shard
+            elif self.peer_weights and st.n_local % 2 == 0:       # an even shard: no k|v or gate|up pair straddles ranks
+                st.gathered = None
+                st.peer_shards = [st.shard if r == self.rank else
+                                  self.heap.view(r, st.shard_off, (st.n_local, H, W), self.dtype)
+                                  for r in range(self.world)]
             else:
                 st.gathered = torch.empty(n_pad, H, W, device=self.device, dtype=self.dtype)
                 st.gathered.copy_(full.data)
@@ -142,16 +153,24 @@ class ShardedEngine:
                     del st.param._hm_grad_sources
 
     # ------------------------------------------------------------------ forward / backward plumbing
+    def _weights(self, st: _BankState, idx: int, n: int) -> torch.Tensor:
+        """Slots ``idx .. idx+n`` as an ``(n, H, W)`` tensor: the gathered copy, or the owner's shard seen through
+        its peer mapping (only this package's own TMA GEMMs ever read that memory)."""
+        if st.gathered is not None:
+            return st.gathered[idx:idx + n]
+        r, j = divmod(idx, st.n_local)
+        return st.peer_shards[r][j:j + n]
+
     def linear(self, x, bank_name: str, idx: int, bias=None):
         st = self.state[bank_name]
-        y = ops.linear(x, st.gathered[idx], sink=st.sinks[idx])
+        y = ops.linear(x, self._weights(st, idx, 1)[0], sink=st.sinks[idx])
         return y if bias is None else y + bias
 
     def linear_pair(self, x, bank_name: str, idx: int):
         """Slots ``idx`` and ``idx+1`` applied as one ``(2H, W)`` projection (one GEMM in each direction)."""
         st = self.state[bank_name]
         H, W = st.spec.matrix_shape
-        return ops.linear(x, st.gathered[idx:idx + 2].view(2 * H, W), sink=st.pair_sinks[idx])
+        return ops.linear(x, self._weights(st, idx, 2).view(2 * H, W), sink=st.pair_sinks[idx])
 
     @contextmanager
     def no_sync(self):
@@ -204,10 +223,14 @@ class ShardedEngine:
             for st in self.state.values():
                 dist.all_gather_into_tensor(st.gathered, st.shard.contiguous())
             return
+        if all(st.gathered is None for st in self.state.values()):
+            return                                   # every bank is read in place through the peer mappings
         if self._copy_table is None:
             ext = self.heap._ext
             tab, units, n = bytearray(), 0, 0
             for st in self.state.values():
+                if st.gathered is None:
+                    continue
                 H, W = st.spec.matrix_shape
                 nbytes = st.n_local * H * W * st.shard.element_size()
                 for r in range(self.world):
@@ -233,7 +256,12 @@ class ShardedEngine:
         if self.banks is None:
             return sd
         for name, st in self.state.items():
-            sd[name] = st.gathered.detach().cpu()
+            if st.gathered is not None:
+                sd[name] = st.gathered.detach().cpu()
+            else:
+                full = torch.empty(st.spec.n_padded, *st.spec.matrix_shape, device=self.device, dtype=self.dtype)
+                dist.all_gather_into_tensor(full, st.shard.detach().contiguous())   # every rank sends its own shard
+                sd[name] = full.cpu()
         return unbank_state_dict(sd, self.banks)
 
     def close(self):

@@ -69,9 +69,13 @@ def scenario_train(mode, optimizer_name, device):
     rank, world = dist.get_rank(), dist.get_world_size()
     torch.manual_seed(0)
     model = CausalLM(_cfg()).to(device, torch.bfloat16)
-    if mode == "fsdp":
+    if mode in ("fsdp", "fsdp-peer"):
         from himuon_b200.parallel.fsdp import ShardedEngine
-        engine = ShardedEngine(model, use_banks=True, timeout_s=30.0)
+        # "fsdp-peer": no gathered copy; the GEMMs read the weights from the owner rank's shard over NVLink
+        engine = ShardedEngine(model, use_banks=True, timeout_s=30.0, peer_weights=(mode == "fsdp-peer"))
+        if mode == "fsdp-peer":
+            assert any(st.gathered is None for st in engine.state.values()) or world == 1
+        mode = "fsdp"
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
         engine = DataParallelEngine(model, timeout_s=30.0)

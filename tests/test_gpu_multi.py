@@ -30,7 +30,8 @@ def test_peer_memory_collectives():
 
 
 @needs2
-@pytest.mark.parametrize("mode,opt", [("fsdp", "himuon"), ("ddp", "himuon"), ("fsdp", "muon-fsdp"), ("fsdp", "adamw")])
+@pytest.mark.parametrize("mode,opt", [("fsdp", "himuon"), ("ddp", "himuon"), ("fsdp", "muon-fsdp"), ("fsdp", "adamw"),
+                                      ("fsdp-peer", "himuon")])
 def test_multi_gpu_training_matches_single_process(mode, opt):
     r = _run(2, "train", mode, opt)
     assert "PARITY OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
