@@ -74,6 +74,8 @@ def build_arg_parser(mode: str) -> argparse.ArgumentParser:
         p.add_argument("--num-decay-steps", type=int, default=400)
         p.add_argument("--min-lr-ratio", type=float, default=0.1)
         p.add_argument("--cpu-offload", action="store_true")
+        p.add_argument("--peer-weights", dest="peer_weights", action="store_true",
+                       help="keep no gathered copy of the banks; the GEMMs read weight tiles from the owner rank over NVLink")
     return p
 
 
@@ -325,7 +327,8 @@ def run_training(args, mode: str) -> dict:
     elif mode == "fsdp":
         from .parallel.fsdp import ShardedEngine
         engine = ShardedEngine(model, use_banks=args.optimizer.lower() in ("himuon", "muon-fsdp"),
-                               cpu_offload=getattr(args, "cpu_offload", False))
+                               cpu_offload=getattr(args, "cpu_offload", False),
+                               peer_weights=getattr(args, "peer_weights", False))
         banks = engine.banks
 
     tokens_per_step = args.batch_size * args.max_length * args.gradient_accumulation_steps * world_size
