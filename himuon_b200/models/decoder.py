@@ -197,7 +197,9 @@ class CausalLM(nn.Module):
             shifted = torch.full_like(labels, -100)
             shifted[:, :-1] = labels[:, 1:]
             head = self._head_weight()
-            loss = ops.linear_cross_entropy(h, head[0], shifted.reshape(-1), sink=head[1], loss_scale=self.loss_scale)
+            # in-forward accumulation of the head's weight gradient only when a backward pass follows this forward
+            scale = self.loss_scale if (self.training and torch.is_grad_enabled()) else None
+            loss = ops.linear_cross_entropy(h, head[0], shifted.reshape(-1), sink=head[1], loss_scale=scale)
         if labels is None or return_logits:
             logits = ops.linear(h, self._head_weight()[0]).view(B, S, -1)
         return CausalLMOutput(loss=loss, logits=logits)

@@ -591,7 +591,7 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, h, w, labels, ignore_index, chunk, sink, param, loss_scale):
+    def forward(ctx, h, w, labels, ignore_index, chunk, sink, param, loss_scale, grad_on):
         e = _ext.ext()
         T, H = h.shape
         V = w.shape[0]
@@ -599,7 +599,9 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
         inv = 1.0 / (labels != ignore_index).sum().clamp(min=1).float()
         loss_sum = torch.zeros((), device=h.device, dtype=torch.float32)
         count = torch.zeros((), device=h.device, dtype=torch.float32)
-        need_grad = h.requires_grad or w.requires_grad or sink is not None
+        # Gradients are produced here, in the forward pass, only when a backward pass will follow: grad mode on and
+        # the hidden states part of a graph.  Under no_grad (evaluation) nothing may touch ``.grad`` or a sink.
+        need_grad = bool(grad_on) and (h.requires_grad or w.requires_grad or sink is not None)
         dh = torch.empty_like(h) if need_grad else None
         direct = loss_scale is not None
         scale = float(loss_scale) if direct else 1.0
@@ -637,11 +639,11 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         if not ctx.has_grad:
-            return (None,) * 8
+            return (None,) * 9
         saved = ctx.saved_tensors
         dh = saved[0] * (g / ctx.scale).to(saved[0].dtype)
         dw = None if ctx.direct else saved[1] * g.to(saved[1].dtype)
-        return dh, dw, None, None, None, None, None, None
+        return dh, dw, None, None, None, None, None, None, None
 
 
 def linear_cross_entropy(h2d, w, labels, ignore_index: int = -100, chunk: int = 4096, sink: GradSink | None = None,
@@ -655,5 +657,7 @@ def linear_cross_entropy(h2d, w, labels, ignore_index: int = -100, chunk: int = 
     """
     if use_kernels(h2d) and w.dtype == torch.bfloat16:
         param = w if isinstance(w, torch.nn.Parameter) else None
-        return _LinearCrossEntropyFn.apply(h2d.contiguous(), w, labels, ignore_index, chunk, sink, param, loss_scale)
+        # autograd.Function.forward always runs with grad mode off, so the caller's mode is passed in
+        return _LinearCrossEntropyFn.apply(h2d.contiguous(), w, labels, ignore_index, chunk, sink, param, loss_scale,
+                                           torch.is_grad_enabled())
     return ref.linear_cross_entropy(h2d, w, labels, ignore_index)

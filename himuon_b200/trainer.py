@@ -262,18 +262,50 @@ class Trainer:
         return total / self.grad_acc
 
     def read_loss(self, loss: torch.Tensor) -> float:
+        """Device-to-host read of the step's loss.  The read synchronises with the device anyway, so the kernels'
+        status word is checked here too: a bounded wait that ran out (a GEMM / attention / Newton-Schulz barrier, a
+        peer-flag handshake of a collective) leaves invalid results behind, and training must stop, not diverge."""
         self.d2h_bytes += loss.numel() * loss.element_size()
-        return float(loss.item())
+        value = float(loss.item())
+        self.check_device_status()
+        return value
+
+    def device_status(self) -> int:
+        """The sticky status word of this rank's kernels (0 = healthy); no synchronisation beyond the read itself."""
+        if self.device.type != "cuda":
+            return 0
+        from . import _ext
+        return int(_ext.ext().status(False))
+
+    def check_device_status(self) -> None:
+        code = self.device_status()
+        if code:
+            raise RuntimeError(f"himuon_b200: a device-side wait timed out on this rank (status code {code}); "
+                               "gradients and parameters of this step are invalid")
 
     @torch.no_grad()
-    def evaluate(self, loader_iter, steps: int) -> float:
+    def evaluate(self, batches, steps: int | None = None) -> float:
+        """Mean loss over fixed evaluation batches (a list collected once, as the reference does,
+        ``train_fsdp.py:147-166``), averaged over the ranks.  Runs under ``no_grad`` in eval mode: no gradient
+        buffer, sink or optimizer state is touched, so a training step after it is unaffected."""
+        if not isinstance(batches, (list, tuple)):          # an iterator: draw `steps` batches from it
+            batches = [next(batches) for _ in range(int(steps or 0))]
+        elif steps is not None:
+            batches = batches[:steps]
+        was_training = self.model.training
         self.model.eval()
-        tot = 0.0
-        for _ in range(steps):
-            batch = self._to_device(next(loader_iter))
-            tot += float(self.model(batch["input_ids"], labels=batch["labels"]).loss.item())
-        self.model.train()
-        return tot / max(1, steps)
+        tot = torch.zeros((), device=self.device, dtype=torch.float32)
+        try:
+            for hb in batches:
+                batch = self._to_device(hb)
+                tot += self.model(batch["input_ids"], labels=batch["labels"]).loss.float()
+        finally:
+            self.model.train(was_training)
+        tot /= max(1, len(batches))
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+            tot /= dist.get_world_size()
+        return float(tot.item())
 
 
 # ------------------------------------------------------------------------------------------- main loop
@@ -336,7 +368,10 @@ def run_training(args, mode: str) -> dict:
         args.num_training_steps = max(1, count_num_training_tokens(model) // tokens_per_step)
     vocab = model.config.vocab_size
     loader = build_dataloader(args, tokenizer, vocab, rank, world_size)
-    eval_iter = iter(build_dataloader(args, tokenizer, vocab, rank, world_size, eval_split=True)) if args.eval_interval else None
+    eval_batches = None
+    if args.eval_interval:        # fixed evaluation set, collected once
+        eval_iter = iter(build_dataloader(args, tokenizer, vocab, rank, world_size, eval_split=True))
+        eval_batches = [next(eval_iter) for _ in range(args.eval_steps)]
 
     optimizer = get_optimizer(args.optimizer, model, args)
     if mode == "fsdp":
@@ -383,15 +418,19 @@ def run_training(args, mode: str) -> dict:
             metrics["tokens_per_sec"] = tokens_per_step / max(1e-9, now - t_step)
             t_step = now
         if args.eval_interval and global_step % args.eval_interval == 0:
-            metrics["eval_loss"] = trainer.evaluate(eval_iter, args.eval_steps)
+            metrics["eval_loss"] = trainer.evaluate(eval_batches)
         if logger is not None:
             logger.log_metrics(metrics)
         last = metrics
         stop = global_step >= args.num_training_steps or budget.is_expired()
         if distributed and world_size > 1:
-            flag = torch.tensor([int(stop)], device=device)
-            dist.broadcast(flag, src=0)
-            stop = bool(flag.item())
+            # one small collective per step carries rank 0's stop decision and every rank's kernel status, so a
+            # rank whose bounded wait ran out makes all ranks raise together instead of training on garbage
+            flag = torch.tensor([int(stop) if is_main else 0, trainer.device_status()], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            stop, bad = bool(flag[0].item()), int(flag[1].item())
+            if bad:
+                raise RuntimeError(f"himuon_b200: a device-side wait timed out on some rank (status code {bad}); stopping")
         if stop:
             log("Stopping training")
             break

@@ -144,3 +144,59 @@ def test_gradient_checkpointing_gives_the_same_gradients_on_the_kernel_path():
         assert a.grad is not None and b.grad is not None, n
         c = _cos(a.grad, b.grad).item()
         assert c > 0.9999, (n, c)
+
+
+def test_evaluate_between_train_steps_does_not_touch_gradients_on_the_kernel_path():
+    """`Trainer.evaluate` runs the fused lm_head + cross-entropy under no_grad: no gradient buffer (they persist,
+    zeroed in place, with the graph-captured optimizer) and no gradient sink may change, and the training step that
+    follows must match a run without the evaluation."""
+    from himuon_b200 import ops
+    from himuon_b200.models import CausalLM
+    from himuon_b200.optim import get_optimizer
+    from himuon_b200.parallel.fsdp import ShardedEngine
+    from himuon_b200.trainer import Trainer
+
+    def batches(n, seed):
+        g = torch.Generator().manual_seed(seed)
+        out = []
+        for _ in range(n):
+            ids = torch.randint(0, 2048, (2, 128), generator=g).pin_memory()
+            out.append({"input_ids": ids, "labels": ids})
+        return out
+
+    def run(with_eval):
+        torch.manual_seed(0)
+        model = CausalLM(_small_cfg("qwen3")).cuda().bfloat16()
+        engine = ShardedEngine(model, use_banks=True)
+        ns = argparse.Namespace(lr=1e-2, weight_decay=0.1, tile_size=128, cuda_graph=True, cuda_graph_warmup=1)
+        opt = get_optimizer("himuon", model, ns)
+        engine.attach_optimizer(opt)
+        tr = Trainer(model, opt, None, engine, 2, torch.device("cuda"))
+        tr.zero_set_to_none = False
+        train = batches(6, 1)
+        tr.train_step(train[0:2])
+        tr.train_step(train[2:4])
+        if with_eval:
+            snap = {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
+            sinks = {k: st.grad_full.clone() for k, st in engine.state.items()}
+            fresh = {k: [s.fresh for s in st.sinks] for k, st in engine.state.items()}
+            ev = tr.evaluate(batches(3, 2))
+            assert ev == ev and model.training
+            for n, p in model.named_parameters():
+                if n in snap:
+                    assert torch.equal(p.grad, snap[n]), n
+            for k, st in engine.state.items():
+                assert torch.equal(st.grad_full, sinks[k]), k
+                assert [s.fresh for s in st.sinks] == fresh[k], k
+        loss = tr.read_loss(tr.train_step(train[4:6]))
+        params = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+        engine.close()
+        return loss, params
+
+    l0, p0 = run(False)
+    l1, p1 = run(True)
+    assert abs(l0 - l1) < 1e-3, (l0, l1)
+    for n in p0:
+        c = _cos(p0[n], p1[n]).item()
+        assert c > 0.99999, (n, c)
+    ops.check_status()
