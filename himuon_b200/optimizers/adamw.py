@@ -16,7 +16,7 @@ from ._multi import AdamTable
 
 
 class AdamW(Optimizer):
-    def __init__(self, params, lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, correct_bias=True):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0, correct_bias=True):
         if lr < 0.0:
             raise ValueError(f"Invalid learning rate: {lr}")
         if not 0.0 <= betas[0] < 1.0 or not 0.0 <= betas[1] < 1.0:
@@ -28,6 +28,11 @@ class AdamW(Optimizer):
     def _signature(self):
         return tuple((p.data_ptr(), p.grad.data_ptr()) for g in self.param_groups for p in g["params"]
                      if p.grad is not None)
+
+    def load_state_dict(self, state_dict):
+        """Restores the state and drops the device entry table (it holds the addresses of the replaced moments)."""
+        super().load_state_dict(state_dict)
+        self._table = AdamTable()
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -69,19 +74,23 @@ class AdamW(Optimizer):
         t = self._table
         if t.sig != sig:
             items = []
+            prior = 0
             for gi, group in enumerate(self.param_groups):
                 for p in group["params"]:
                     if p.grad is None:
                         continue
                     st = self.state[p]
+                    if "exp_avg" in st:                 # moments restored by load_state_dict: keep their step count
+                        prior = max(prior, int(st.get("step", 0)))
                     if "exp_avg" not in st:
                         st["step"] = 0
                         st["exp_avg"] = torch.zeros_like(p.grad)
                         st["exp_avg_sq"] = torch.zeros_like(p.grad)
                     items.append((p.data, p.grad.contiguous() if not p.grad.is_contiguous() else p.grad,
                                   st["exp_avg"], st["exp_avg_sq"], gi))
-            t.build(items, len(self.param_groups), device)
+            t.build(items, len(self.param_groups), device, start_step=prior)
             t.sig = sig
+        t.begin_hyper()
         for gi, group in enumerate(self.param_groups):
             t.hyper_host[gi, 0] = group["lr"]
             t.hyper_host[gi, 1] = group["weight_decay"]

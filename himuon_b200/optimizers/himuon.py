@@ -32,6 +32,7 @@ import torch
 from torch.optim import Optimizer
 
 from ..ops import ns as ns_ops
+from ._multi import PinnedHyper
 from ..ops import reference as ref
 
 try:  # DTensor support is optional
@@ -99,8 +100,8 @@ class HiMuon(Optimizer):
         # device-side execution state (CUDA only)
         self._exec = None                # list of per-bucket launch records
         self._adam_exec = None
+        self._hyper = None               # PinnedHyper: rotating pinned rows + the device table the kernels read
         self._hyper_dev = None
-        self._hyper_host = None
         self._adam_step = None
         self._ns_workspace = ns_ops.NSWorkspace()
         self._ptr_signature = None
@@ -148,6 +149,13 @@ class HiMuon(Optimizer):
         self._adam_exec = None
         self._ptr_signature = None
         self._ns_workspace.clear()
+
+    def load_state_dict(self, state_dict):
+        """Restores the state and drops every device entry table: they hold raw addresses of the momentum and
+        moment tensors that ``load_state_dict`` has just replaced."""
+        super().load_state_dict(state_dict)
+        self._invalidate_plan_cache()
+        self._adam_step = None
 
     def xlayer_plan(self) -> list[dict]:
         """Snapshot of the cross-layer bucket plan (``[]`` before the first step and after
@@ -385,8 +393,8 @@ class HiMuon(Optimizer):
         from .._ext import ext
         e = ext()
         n_groups = len(self.param_groups)
-        self._hyper_host = torch.zeros(n_groups, 8, dtype=torch.float32).pin_memory()
-        self._hyper_dev = torch.zeros(n_groups, 8, dtype=torch.float32, device=device)
+        self._hyper = PinnedHyper(n_groups, device)
+        self._hyper_dev = self._hyper.dev
         if self._adam_step is None:
             # resume the shared step counter from a loaded state dict when there is one
             prior = [st["step"] for st in self.state.values() if isinstance(st, dict) and "step" in st]
@@ -477,13 +485,13 @@ class HiMuon(Optimizer):
         self._pending_updates = [(m.param, None, m.group_idx) for b in self._cached_plan for m in b["_entries"]]
 
     def _refresh_hyper(self):
-        h = self._hyper_host
+        h = self._hyper.begin()
         for gi, group in enumerate(self.param_groups):
             h[gi, 0] = group["lr"]
             h[gi, 1] = group["weight_decay"]
             h[gi, 2], h[gi, 3] = group["adamw_betas"]
             h[gi, 4] = group["adamw_eps"]
-        self._hyper_dev.copy_(h, non_blocking=True)
+        self._hyper.commit()
 
     def _launch_all(self, timing: list | None = None):
         from .._ext import ext

@@ -44,6 +44,11 @@ class Muon(Optimizer):
     def _data(self, p):
         return p.data
 
+    def load_state_dict(self, state_dict):
+        """Restores the state and drops the device entry table (it holds the addresses of the replaced moments)."""
+        super().load_state_dict(state_dict)
+        self._table = AdamTable()
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = None
@@ -94,19 +99,23 @@ class Muon(Optimizer):
                         if p.grad is not None)
             if t.sig != sig:
                 items = []
+                prior = 0
                 for gi, group in groups:
                     for p in group["params"]:
                         if p.grad is None:
                             continue
                         g = self._grad(p)
                         st = self.state[p]
+                        if "moment1" in st:             # restored by load_state_dict: keep the step count
+                            prior = max(prior, int(st.get("step", 0)))
                         if "moment1" not in st:
                             st["step"] = 0
                             st["moment1"] = torch.zeros_like(g)
                             st["moment2"] = torch.zeros_like(g)
                         items.append((self._data(p), g, st["moment1"], st["moment2"], gi))
-                t.build(items, len(self.param_groups), first.device if not hasattr(first, "to_local") else self._data(first).device)
+                t.build(items, len(self.param_groups), self._data(first).device, start_step=prior)
                 t.sig = sig
+            t.begin_hyper()
             for gi, group in groups:
                 t.hyper_host[gi, 0] = group["lr"]
                 t.hyper_host[gi, 1] = group["weight_decay"]
