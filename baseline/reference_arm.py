@@ -53,7 +53,11 @@ def run(args, timed_region, host_batches, init_dist, barrier_sync):
     mesh = init_device_mesh("cuda", (world,), mesh_dim_names=("dp",))
     config = _qwen3_config(args.model)
     model = AutoModelForCausalLM.from_config(config)
-    model.gradient_checkpointing_enable()
+    # the reference's train_fsdp.py enables gradient checkpointing by default (--gradient-checkpointing, on);
+    # `--activation-checkpointing off` is its --no-gradient-checkpointing
+    checkpointing = getattr(args, "activation_checkpointing", None) != "off"
+    if checkpointing:
+        model.gradient_checkpointing_enable()
     model.config.use_cache = False
     model.to(device=device, dtype=torch.bfloat16)
     model, banks = wrap_with_banks(model, Qwen3BankScheme(), world_size=world)
@@ -61,7 +65,8 @@ def run(args, timed_region, host_batches, init_dist, barrier_sync):
     fully_shard(model, mesh=mesh, mp_policy=mp_policy, offload_policy=OffloadPolicy())
     release_pre_shard_refs(banks)
     torch.cuda.empty_cache()
-    opt_args = argparse.Namespace(lr=LR, weight_decay=WD, tile_size=args.tile, cuda_graph=False)
+    ref_graph = bool(getattr(args, "reference_cuda_graph", False))
+    opt_args = argparse.Namespace(lr=LR, weight_decay=WD, tile_size=args.tile, cuda_graph=ref_graph)
     optimizer = get_optimizer("himuon", model, opt_args)
     scheduler = get_wsd_schedule(optimizer, num_warmup_steps=100, num_stable_steps=0, num_decay_steps=400,
                                  num_training_steps=10000, min_lr_ratio=0.1, decay_type="cosine", warmup_type="linear")
@@ -69,6 +74,8 @@ def run(args, timed_region, host_batches, init_dist, barrier_sync):
     grad_acc = args.grad_acc
     n_total = args.warmup + args.steps
     hb = host_batches(config.vocab_size, n_total + 1 + args.steps, grad_acc, args.micro_batch, args.seq_len, rank)
+
+    opt_events = []
 
     def train_step(batches, from_host):
         total = None
@@ -80,17 +87,28 @@ def run(args, timed_region, host_batches, init_dist, barrier_sync):
             loss = out.loss / grad_acc
             loss.backward()
             total = loss.detach() if total is None else total + loss.detach()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
         optimizer.step()
+        ev1.record()
+        opt_events.append((ev0, ev1))
         scheduler.step()
-        optimizer.zero_grad(set_to_none=True)
+        optimizer.zero_grad(set_to_none=not ref_graph)
         return total
 
     dev = [[{k: v.to(device) for k, v in mb.items()} for mb in step] for step in hb[:n_total]]
     for i in range(args.warmup):
         train_step(dev[i], False)
     tokens_per_step = args.micro_batch * args.seq_len * grad_acc * world
+    opt_events.clear()
     ms = timed_region(lambda i: train_step(dev[args.warmup + i], False), args.steps)
     value = tokens_per_step * args.steps / (ms / 1e3)
+    # device time of its own optimizer.step(), mean over the timed steps, max over ranks
+    opt_ms = sum(a.elapsed_time(b) for a, b in opt_events) / max(1, len(opt_events))
+    if world > 1:
+        t = torch.tensor([opt_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        opt_ms = float(t.item())
     e2e = None
     if not args.no_e2e:
         float(train_step(hb[n_total], True).item())
@@ -108,8 +126,9 @@ def run(args, timed_region, host_batches, init_dist, barrier_sync):
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model, "global_batch": args.micro_batch * grad_acc * world, "seq_len": args.seq_len,
-                       "parallelism": f"fsdp2-banks{world}", "optimizer": f"reference himuon tile {args.tile}, cuda_graph off",
-                       "activation_checkpointing": True},
+                       "parallelism": f"fsdp2-banks{world}", "optimizer": f"reference himuon tile {args.tile}, cuda_graph {'on' if ref_graph else 'off'}",
+                       "activation_checkpointing": checkpointing},
+            "optimizer_step_ms": opt_ms,
             "e2e": e2e, "gpu_launches": 0,
         }
     barrier_sync()

@@ -56,6 +56,12 @@ def parse():
     p.add_argument("--engine", type=str, default="fsdp", choices=["fsdp", "ddp"],
                    help="fsdp: bank-sharded engine (headline); ddp: replicated parameters + fused all-reduce")
     p.add_argument("--optimizer", type=str, default="himuon", help="himuon | muon-fsdp | muon | adamw (headline: himuon)")
+    p.add_argument("--activation-checkpointing", type=str, default=None, choices=["on", "off"],
+                   help="per-layer recomputation in backward, honoured by both arms.  Default: each arm's own stock "
+                        "setting (ours off, the reference's train_fsdp.py default on); pass the same value to both "
+                        "arms for a like-for-like comparison")
+    p.add_argument("--reference-cuda-graph", action="store_true",
+                   help="reference arm only: construct its HiMuon with cuda_graph=True (its FSDP default is False)")
     return p.parse_args()
 
 
@@ -130,6 +136,9 @@ def run_ours(args):
     cfg = get_config(args.model)
     with torch.device(device):
         model = CausalLM(cfg).to(torch.bfloat16)
+    checkpointing = args.activation_checkpointing == "on"
+    if checkpointing:
+        model.gradient_checkpointing_enable()
     if args.engine == "fsdp":
         engine = ShardedEngine(model, use_banks=args.optimizer in ("himuon", "muon-fsdp"), peer_weights=args.peer_weights)
     else:
@@ -162,21 +171,17 @@ def run_ours(args):
     ops.check_status()
     value = tokens_per_step * args.steps / (ms / 1e3)
 
-    # optimizer step alone (device time of one step, max over ranks)
-    opt_ms = None
-    try:
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        engine.finish_backward()
-        barrier_sync()
-        ev0.record()
-        optimizer.step()
-        ev1.record()
-        barrier_sync()
-        from himuon_b200.utils import max_over_ranks
-        opt_ms = max_over_ranks(ev0.elapsed_time(ev1))
-        engine.zero_grad(set_to_none=False)
-    except Exception:
-        opt_ms = None
+    # optimizer step alone (device time of one step on the zeroed gradients left by the last step, max over ranks)
+    from himuon_b200.utils import max_over_ranks
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    engine.finish_backward()
+    barrier_sync()
+    ev0.record()
+    optimizer.step()
+    ev1.record()
+    barrier_sync()
+    opt_ms = max_over_ranks(ev0.elapsed_time(ev1))
+    engine.zero_grad(set_to_none=False)
 
     e2e = None
     if not args.no_e2e:
@@ -204,7 +209,7 @@ def run_ours(args):
                        "parallelism": (f"fsdp-banks{world}" + ("-peer-weights" if args.peer_weights else "")) if args.engine == "fsdp" else f"dp{world}",
                        "optimizer": f"{args.optimizer} tile {args.tile}, lr {ns.lr}, wd {WD}, cuda graph",
                        "forward_backward": "eager" if args.no_step_graph else "micro-batch CUDA graphs (public Trainer option)",
-                       "activation_checkpointing": False,
+                       "activation_checkpointing": checkpointing,
                        "l2": "no flush: each step streams >8 GB of weights and activations (L2 is 126 MB)"},
             "optimizer_step_ms": opt_ms,
             "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": launches, "impl": "ours",
