@@ -18,7 +18,8 @@ static bool is_f32(const at::Tensor& t) { return t.scalar_type() == at::kFloat; 
 
 // out = alpha * op(a) @ op(b) + beta * aux.   a: (.., M, K) or (.., K, M) when trans_a; b: (.., K, N) or (.., N, K) when trans_b.
 static void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, const c10::optional<at::Tensor>& aux,
-                 bool trans_a, bool trans_b, double alpha, double beta, bool round_acc, int64_t max_ctas) {
+                 bool trans_a, bool trans_b, double alpha, double beta, bool round_acc, int64_t max_ctas,
+                 bool symmetric) {
   HM_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda(), "gemm operands must be CUDA tensors");
   HM_CHECK(is_bf16(a) && is_bf16(b), "gemm operands must be bf16");
   HM_CHECK(is_bf16(out) || is_f32(out), "gemm output must be bf16 or fp32");
@@ -49,6 +50,8 @@ static void gemm(const at::Tensor& a, const at::Tensor& b, at::Tensor& out, cons
   g.out_fp32 = is_f32(out) ? 1 : 0;
   g.round_acc = round_acc ? 1 : 0;
   g.max_ctas = static_cast<int>(max_ctas);
+  g.symmetric = symmetric ? 1 : 0;
+  if (symmetric) HM_CHECK(g.M == g.N, "gemm: a symmetric output must be square");
   if (aux.has_value() && beta != 0.0) {
     const at::Tensor& x = aux.value();
     HM_CHECK(x.scalar_type() == out.scalar_type() && x.dim() == nd && x.stride(nd - 1) == 1, "gemm aux must match the output dtype/rank");
@@ -252,7 +255,7 @@ static int64_t status(bool reset) { return himuon::read_status_word(reset); }
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("aux") = py::none(), py::arg("trans_a") = false,
         py::arg("trans_b") = false, py::arg("alpha") = 1.0, py::arg("beta") = 0.0, py::arg("round_acc") = false,
-        py::arg("max_ctas") = 0);
+        py::arg("max_ctas") = 0, py::arg("symmetric") = false);
   m.def("momentum_tile", &momentum_tile);
   m.def("untile_apply", &untile_apply);
   m.def("ns_normalize", &ns_normalize, py::arg("tiles"), py::arg("n_tiles"), py::arg("tile_elems"), py::arg("eps"),

@@ -23,8 +23,56 @@ struct GemmDev {
   int reduce_out;   // pair kernel, C += alpha*acc (aux == C, beta == 1; fp32 or bf16): tiles add into C with TMA reductions
   int stream_k;     // with reduce_out: every CTA pair takes an equal, contiguous range of (tile, k-block) units and
                     // adds each partial tile into C, so no wave of tiles is left partly idle
+  // Symmetric output (C = C^T by construction: X X^T, c A A + b A with A symmetric; one-CTA kernel, bf16 out):
+  // tiles that lie entirely above the diagonal are not computed; tiles entirely below it are also stored transposed.
+  int sym;          // 1: symmetric mode
+  int sym_tiles;    // computed tiles per batch entry
   int* status;
 };
+
+// Tile coordinates of work item `tile`.  In symmetric mode (tile width BN = R * BM) column block nt keeps the row
+// blocks mt >= nt*R, enumerated mt-fastest; a tile with mt >= (nt+1)*R has no entry on or above the diagonal and
+// its transpose covers exactly entries of tiles that were dropped.
+struct TileCoord { int b, mt, nt; bool mirror; };
+__device__ __forceinline__ TileCoord decode_tile(const GemmDev& p, int tile, int R) {
+  TileCoord t;
+  if (!p.sym) {
+    const int per = p.tiles_m * p.tiles_n;
+    t.b = tile / per;
+    const int r = tile - t.b * per;
+    t.mt = r % p.tiles_m;
+    t.nt = r / p.tiles_m;
+    t.mirror = false;
+    return t;
+  }
+  t.b = tile / p.sym_tiles;
+  int k = tile - t.b * p.sym_tiles;
+  int nt = 0;
+  for (;;) {
+    const int cnt = p.tiles_m - nt * R;
+    if (k < cnt || nt + 1 >= p.tiles_n) break;
+    k -= cnt;
+    ++nt;
+  }
+  t.nt = nt;
+  t.mt = nt * R + k;
+  t.mirror = t.mt >= (nt + 1) * R;
+  return t;
+}
+
+// Transposed store of eight consecutive bf16 columns of one tile row: element j goes to C[row0 + j][col] (rows and
+// col bounded by n).  The 32 lanes of a warp hold 32 consecutive `col`s, so each store instruction writes 64
+// contiguous bytes.
+__device__ __forceinline__ void mirror_store8(__nv_bfloat16* C, long long ldc, int row0, int col, int n,
+                                              const uint32_t (&o)[4]) {
+  if (col >= n) return;
+  unsigned short* base = reinterpret_cast<unsigned short*>(C) + static_cast<long long>(row0) * ldc + col;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    if (row0 + 2 * t < n) base[static_cast<long long>(2 * t) * ldc] = static_cast<unsigned short>(o[t] & 0xFFFFu);
+    if (row0 + 2 * t + 1 < n) base[static_cast<long long>(2 * t + 1) * ldc] = static_cast<unsigned short>(o[t] >> 16);
+  }
+}
 
 struct WorkItem { int tile, kb0, kb1, slice, tail; bool split; };
 __device__ __forceinline__ WorkItem decode_item(const GemmDev& p, int item) {
@@ -119,7 +167,8 @@ template <int BN, bool OUT_FP32>
 __device__ __forceinline__ void epilogue_tile_tma(const CUtensorMap* tmC, uint8_t* sC, uint32_t t_row, int row_in_tile,
                                                   int m0, int n0, int b, const void* aux, long long aux_row_off,
                                                   int M, int N, float alpha, float beta, int round_acc,
-                                                  uint32_t& slab_seq, bool issuer, bool reduce_add = false) {
+                                                  uint32_t& slab_seq, bool issuer, bool reduce_add = false,
+                                                  __nv_bfloat16* mirror_c = nullptr, long long mirror_ld = 0) {
   constexpr int SW = OUT_FP32 ? 32 : 64;
   constexpr int SLABS = BN / SW;
   const bool row_ok = (m0 + row_in_tile) < M;
@@ -163,6 +212,7 @@ __device__ __forceinline__ void epilogue_tile_tma(const CUtensorMap* tmC, uint8_
           }
           const int j = ch * 4 + q;
           *reinterpret_cast<uint4*>(my_row + ((j ^ (row_in_tile & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          if (mirror_c != nullptr) mirror_store8(mirror_c, mirror_ld, col + j * 8, m0 + row_in_tile, N, o);
         }
       }
     }

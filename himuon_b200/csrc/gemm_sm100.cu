@@ -68,8 +68,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int tiles_per_batch = p.tiles_m * p.tiles_n;
-
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -80,11 +78,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
         const WorkItem w = decode_item(p, item);
-        const int tile = w.tile;
-        const int b = tile / tiles_per_batch;
-        const int r = tile - b * tiles_per_batch;
-        const int mt = r % p.tiles_m;
-        const int nt = r / p.tiles_m;
+        const TileCoord tc = decode_tile(p, w.tile, BN / BM);
+        const int b = tc.b, mt = tc.mt, nt = tc.nt;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
           uint8_t* sA = smem + stage * STAGE_BYTES;
@@ -160,10 +155,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t pf_seq = 0;
       auto prefetch_next = [&]() {
         while (pf_item < p.total_items) {
-          const int b = pf_item / tiles_per_batch;
-          const int r = pf_item - b * tiles_per_batch;
-          const int mt = r % p.tiles_m;
-          const int nt = r / p.tiles_m;
+          const TileCoord tc = decode_tile(p, pf_item, BN / BM);
+          const int b = tc.b, mt = tc.mt, nt = tc.nt;
           const int col = nt * BN + pf_sl * SW;
           if (col < p.N) {
             const uint32_t buf = pf_seq & 3;
@@ -185,10 +178,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t g = 0;                        // slabs finished by this CTA
       bool ok = true;
       for (int item = blockIdx.x; ok && item < p.total_items; item += gridDim.x) {
-        const int b = item / tiles_per_batch;
-        const int r = item - b * tiles_per_batch;
-        const int mt = r % p.tiles_m;
-        const int nt = r / p.tiles_m;
+        const TileCoord tc = decode_tile(p, item, BN / BM);
+        const int b = tc.b, mt = tc.mt, nt = tc.nt;
+        __nv_bfloat16* mirror_c = tc.mirror ? reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(b) * p.strideC : nullptr;
         if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, p.status, 3)) break;
         tc_fence_after();
         const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(acc * BN);
@@ -218,6 +210,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 o[t] = pack_bf16x2(f0 + p.beta * bf16_lo(ew4[t]), f1 + p.beta * bf16_hi(ew4[t]));
               }
               *cell = make_uint4(o[0], o[1], o[2], o[3]);
+              if (mirror_c != nullptr) mirror_store8(mirror_c, p.ldc, col + (ch * 4 + q) * 8, mt * BM + row_in_tile, p.N, o);
             }
           }
           fence_proxy_async_smem();
@@ -241,11 +234,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     } else
     for (int item = blockIdx.x; item < p.total_items; item += gridDim.x) {
       const WorkItem w = decode_item(p, item);
-      const int tile = w.tile;
-      const int b = tile / tiles_per_batch;
-      const int r = tile - b * tiles_per_batch;
-      const int mt = r % p.tiles_m;
-      const int nt = r / p.tiles_m;
+      const TileCoord tc = decode_tile(p, w.tile, BN / BM);
+      const int b = tc.b, mt = tc.mt, nt = tc.nt;
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag, p.status, 3)) break;
       tc_fence_after();
       if (p.tma_store) {
@@ -257,7 +247,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                       p.alpha, p.beta, p.round_acc, slab_seq, issuer);
         else
           epilogue_tile_tma<BN, false>(&tmC, sC, t_acc, row_in_tile, mt * BM, nt * BN, b, p.aux, aux_row, p.M, p.N,
-                                       p.alpha, p.beta, p.round_acc, slab_seq, issuer);
+                                       p.alpha, p.beta, p.round_acc, slab_seq, issuer, false,
+                                       tc.mirror ? reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(b) * p.strideC : nullptr,
+                                       p.ldc);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -457,7 +449,15 @@ static void launch_gemm(const GemmArgs& a, cudaStream_t stream) {
     const uint32_t boxX[3] = {64, BM, 1};
     tmX = make_tmap(a.aux, 3, dimsX, strX, boxX, 2, true);
   }
-  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batch;
+  long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batch;
+  // Symmetric output: needs square bf16 C reachable by TMA stores and a tile width that is a whole number of tile
+  // heights; otherwise every tile is computed (same result).
+  p.sym = (a.symmetric && a.M == a.N && !a.out_fp32 && p.tma_store && BN % BM == 0 && p.tiles_n > 1) ? 1 : 0;
+  p.sym_tiles = 0;
+  if (p.sym) {
+    for (int nt = 0; nt < p.tiles_n; ++nt) p.sym_tiles += p.tiles_m - nt * (BN / BM);
+    total = static_cast<long long>(p.sym_tiles) * a.batch;
+  }
   int sms = a.max_ctas > 0 ? a.max_ctas : num_sms();
   p.full_items = p.total_items = static_cast<int>(total);
   p.nslices = 1;

@@ -34,6 +34,8 @@ struct GemmArgs {
   int out_fp32 = 0;
   int round_acc = 0;
   int max_ctas = 0;   // 0 = one CTA per SM
+  int symmetric = 0;  // the caller guarantees C = C^T (X X^T, or c A A + b A with A symmetric): the one-CTA kernel then
+                      // computes only the tiles that touch the lower triangle and mirrors the rest
 };
 void gemm_bf16(const GemmArgs& args, cudaStream_t stream);
 // CTA-pair (cta_group::2) variant for 256 x 256 tiles; gemm_bf16 dispatches to it when gemm2_supported().

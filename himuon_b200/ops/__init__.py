@@ -49,8 +49,10 @@ def check_status() -> None:
 
 # ------------------------------------------------------------------------------------------- GEMM
 def gemm(a, b, *, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, aux=None, out=None,
-         out_dtype=None, round_acc=False, max_ctas=0):
-    """``alpha * op(a) @ op(b) + beta * aux`` for 2-D or batched 3-D operands (no autograd)."""
+         out_dtype=None, round_acc=False, max_ctas=0, symmetric=False):
+    """``alpha * op(a) @ op(b) + beta * aux`` for 2-D or batched 3-D operands (no autograd).  ``symmetric``: the caller
+    guarantees a symmetric result (``X X^T``; ``c A A + b A`` with ``A`` symmetric), which lets the kernel compute one
+    triangle of tiles and mirror it."""
     if use_kernels(a):
         M = a.shape[-1] if trans_a else a.shape[-2]
         N = b.shape[-2] if trans_b else b.shape[-1]
@@ -60,7 +62,8 @@ def gemm(a, b, *, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, aux=None, o
             a = a.contiguous()
         if b.stride(-1) != 1:
             b = b.contiguous()
-        _ext.ext().gemm(a, b, out, aux, trans_a, trans_b, float(alpha), float(beta), bool(round_acc), int(max_ctas))
+        _ext.ext().gemm(a, b, out, aux, trans_a, trans_b, float(alpha), float(beta), bool(round_acc), int(max_ctas),
+                        bool(symmetric))
         _count()
         return out
     A = a.transpose(-2, -1) if trans_a else a

@@ -7,7 +7,9 @@
 * the tile-resident fused kernel (one CTA per tile, operands in shared memory, accumulators
   in TMEM) for tiles with at most 128 rows and 64..256 columns, and
 * otherwise a batched three-GEMM iteration on the persistent tcgen05 GEMM with fused
-  epilogues (``A = X X^T``; ``B = c A A + b A``; ``X = bf16(B X) + a X``), which handles any
+  epilogues (``A = X X^T``; ``B = c A A + b A``; ``X = bf16(B X) + a X``; the two symmetric
+  products compute only the tiles that touch the lower triangle and mirror them, as the
+  reference's ``XXT`` / ``ba_plus_cAA`` kernels do), which handles any
   shape whose sides are multiples of 8, tall tiles included (no transpose copy: the GEMM
   reads either operand in either major).
 
@@ -82,12 +84,12 @@ def ns_inplace_cuda(X: torch.Tensor, steps: int = 5, eps: float = 1e-7, workspac
     wide = m <= n
     for _ in range(steps):
         if wide:
-            gemm(cur, cur, trans_b=True, out=A)                                   # A = X X^T        (m x m)
-            gemm(A, A, trans_b=True, alpha=C_COEF, beta=B_COEF, aux=A, out=Bm)     # B = c A A + b A
+            gemm(cur, cur, trans_b=True, out=A, symmetric=True)                   # A = X X^T        (m x m)
+            gemm(A, A, trans_b=True, alpha=C_COEF, beta=B_COEF, aux=A, out=Bm, symmetric=True)  # B = c A A + b A
             gemm(Bm, cur, alpha=1.0, beta=A_COEF, aux=cur, out=nxt, round_acc=True)  # X' = B X + a X
         else:
-            gemm(cur, cur, trans_a=True, out=A)                                   # A = X^T X        (n x n)
-            gemm(A, A, trans_b=True, alpha=C_COEF, beta=B_COEF, aux=A, out=Bm)
+            gemm(cur, cur, trans_a=True, out=A, symmetric=True)                   # A = X^T X        (n x n)
+            gemm(A, A, trans_b=True, alpha=C_COEF, beta=B_COEF, aux=A, out=Bm, symmetric=True)
             gemm(cur, Bm, alpha=1.0, beta=A_COEF, aux=cur, out=nxt, round_acc=True)  # X' = X B + a X
         cur, nxt = nxt, cur
     if cur is not X:

@@ -30,8 +30,18 @@ def _close(out, ref, atol, rtol):
     ref = ref.float()
     err = (out - ref).abs()
     tol = atol + rtol * ref.abs()
-    bad = (err > tol).float().mean().item()
-    assert bad < 1e-3, f"{bad:.4%} elements out of tolerance; max err {err.max().item():.4g}, ref max {ref.abs().max().item():.4g}"
+    # Every element is checked.  A few per hundred thousand may exceed the tolerance (rounding of a value that sits on
+    # a bf16 boundary), none may exceed it four-fold, and no single row or column may collect the outliers: a wrong
+    # boundary row or tile edge fails even when it is a vanishing share of the matrix.
+    over = err > tol
+    bad = over.float().mean().item()
+    assert bad <= 1e-5, f"{bad:.4%} elements out of tolerance; max err {err.max().item():.4g}, ref max {ref.abs().max().item():.4g}"
+    worst = (err / tol).max().item()
+    assert worst <= 4.0, f"an element is {worst:.1f}x outside the tolerance (max err {err.max().item():.4g})"
+    if over.dim() >= 2 and over.any():
+        per_row = over.reshape(-1, over.shape[-1]).float().mean(dim=1).max().item()
+        per_col = over.reshape(-1, over.shape[-2], over.shape[-1]).float().mean(dim=1).max().item()
+        assert per_row <= 0.02 and per_col <= 0.02, f"outliers concentrate in one row/column ({per_row:.2%} / {per_col:.2%})"
 
 
 @pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, False), (True, True)])
