@@ -51,6 +51,10 @@ def parse():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--peer-weights", action="store_true",
                    help="no gathered copy of the banks: the GEMMs read weight tiles from the owner rank over NVLink")
+    p.add_argument("--fsdp-weights", type=str, default="gathered", choices=["gathered", "ring", "peer"],
+                   help="bank working copy: full gathered copy (default), two-slot staging ring, or peer reads")
+    p.add_argument("--fsdp-grads", type=str, default="replicated", choices=["replicated", "sharded"],
+                   help="bank gradient accumulation: full buffer per rank (default) or per-group reduce-scatter")
     p.add_argument("--no-step-graph", action="store_true",
                    help="run forward/backward eagerly instead of replaying the captured micro-batch CUDA graphs")
     p.add_argument("--engine", type=str, default="fsdp", choices=["fsdp", "ddp"],
@@ -140,7 +144,9 @@ def run_ours(args):
     if checkpointing:
         model.gradient_checkpointing_enable()
     if args.engine == "fsdp":
-        engine = ShardedEngine(model, use_banks=args.optimizer in ("himuon", "muon-fsdp"), peer_weights=args.peer_weights)
+        weights = "peer" if args.peer_weights else args.fsdp_weights
+        engine = ShardedEngine(model, use_banks=args.optimizer in ("himuon", "muon-fsdp", "adamw"), weights=weights,
+                               grads=args.fsdp_grads)
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
         engine = DataParallelEngine(model)
@@ -206,7 +212,7 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model, "global_batch": args.micro_batch * args.grad_acc * world,
                        "seq_len": args.seq_len, "micro_batch_per_gpu": args.micro_batch, "grad_acc": args.grad_acc,
-                       "parallelism": (f"fsdp-banks{world}" + ("-peer-weights" if args.peer_weights else "")) if args.engine == "fsdp" else f"dp{world}",
+                       "parallelism": (f"fsdp-banks{world}" + (f" weights={engine.weights_mode} grads={engine.grads_mode}" if world > 1 else "")) if args.engine == "fsdp" else f"dp{world}",
                        "optimizer": f"{args.optimizer} tile {args.tile}, lr {ns.lr}, wd {WD}, cuda graph",
                        "forward_backward": "eager" if args.no_step_graph else "micro-batch CUDA graphs (public Trainer option)",
                        "activation_checkpointing": checkpointing,

@@ -5,9 +5,10 @@
 //   allreduce_symm   : one-launch two-shot all-reduce (reduce-scatter by peer loads, all-gather by
 //                      peer stores) with the average / cast fused; replaces the DDP reducer's
 //                      bucketed NCCL all-reduce (reference: train_ddp.py:90, implicit)
-//   reduce_replicas  : out = scale * sum_r replica_r, the owner-side half of a reduce-scatter for
-//                      optimizers that need a plain `.grad` (HiMuon fuses this step into
-//                      momentum_tile instead)
+//   reduce_replicas  : out = beta * out + scale * sum_r replica_r, the owner-side half of a
+//                      reduce-scatter: for optimizers that need a plain `.grad` (HiMuon fuses this
+//                      step into momentum_tile instead), and for the per-layer-group gradient
+//                      reduce-scatter of the sharded-gradient mode (beta = 1 accumulates micro-batches)
 //   multi_copy       : one launch that pulls many (peer -> local) segments; the bank all-gather
 //
 // Every wait on a peer flag is bounded: on expiry the kernel records status 6 and returns, so a
@@ -134,7 +135,7 @@ void allreduce_symm(const CommPeers& peers, const CommBufs& bufs, long long n_el
 // ------------------------------------------------------------------------------------------------ reduce replicas
 template <typename T>
 __global__ void __launch_bounds__(512)
-reduce_replicas_kernel(CommBufs srcs, int n_src, T* __restrict__ out, long long n_elems, float scale) {
+reduce_replicas_kernel(CommBufs srcs, int n_src, T* __restrict__ out, long long n_elems, float scale, float beta) {
   constexpr int VEC = 16 / sizeof(T);
   const long long n_vec = n_elems / VEC;
   for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < n_vec;
@@ -153,20 +154,33 @@ reduce_replicas_kernel(CommBufs srcs, int n_src, T* __restrict__ out, long long 
         for (int q = 0; q < 4; ++q) acc[q] += __uint_as_float(w[q]);
       }
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] *= scale;
+    if (beta != 0.f) {                                   // accumulate onto what `out` already holds
+      const uint4 x = reinterpret_cast<const uint4*>(out)[v];
+      const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+      if (sizeof(T) == 2) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { acc[2 * q] += beta * bf16_lo(w[q]); acc[2 * q + 1] += beta * bf16_hi(w[q]); }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[q] += beta * __uint_as_float(w[q]);
+      }
+    }
     uint4 o;
     if (sizeof(T) == 2) {
-      o.x = pack_bf16x2(acc[0] * scale, acc[1] * scale); o.y = pack_bf16x2(acc[2] * scale, acc[3] * scale);
-      o.z = pack_bf16x2(acc[4] * scale, acc[5] * scale); o.w = pack_bf16x2(acc[6] * scale, acc[7] * scale);
+      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
     } else {
-      o.x = __float_as_uint(acc[0] * scale); o.y = __float_as_uint(acc[1] * scale);
-      o.z = __float_as_uint(acc[2] * scale); o.w = __float_as_uint(acc[3] * scale);
+      o.x = __float_as_uint(acc[0]); o.y = __float_as_uint(acc[1]);
+      o.z = __float_as_uint(acc[2]); o.w = __float_as_uint(acc[3]);
     }
     reinterpret_cast<uint4*>(out)[v] = o;
   }
 }
 
 void reduce_replicas(const CommBufs& srcs, int n_src, void* out, long long n_elems, int is_fp32, float scale,
-                     cudaStream_t s) {
+                     cudaStream_t s, float beta) {
   if (n_elems <= 0) return;
   const int vec = is_fp32 ? 4 : 8;
   if (n_elems % vec) throw std::runtime_error("himuon reduce_replicas: element count must be a multiple of 16 bytes");
@@ -174,9 +188,9 @@ void reduce_replicas(const CommBufs& srcs, int n_src, void* out, long long n_ele
   const long long cap = static_cast<long long>(num_sms()) * 2;
   if (blocks > cap) blocks = cap;
   if (is_fp32)
-    reduce_replicas_kernel<float><<<static_cast<int>(blocks), 512, 0, s>>>(srcs, n_src, reinterpret_cast<float*>(out), n_elems, scale);
+    reduce_replicas_kernel<float><<<static_cast<int>(blocks), 512, 0, s>>>(srcs, n_src, reinterpret_cast<float*>(out), n_elems, scale, beta);
   else
-    reduce_replicas_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 512, 0, s>>>(srcs, n_src, reinterpret_cast<__nv_bfloat16*>(out), n_elems, scale);
+    reduce_replicas_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 512, 0, s>>>(srcs, n_src, reinterpret_cast<__nv_bfloat16*>(out), n_elems, scale, beta);
 }
 
 // ------------------------------------------------------------------------------------------------ multi copy

@@ -163,8 +163,9 @@ struct CopySeg { const void* src; void* dst; long long bytes; long long unit_beg
 void peer_barrier(const CommPeers& peers, int* epoch_local, cudaStream_t s);
 void allreduce_symm(const CommPeers& peers, const CommBufs& bufs, long long n_elems, int is_fp32, float scale,
                     int* epoch_local, int max_blocks, cudaStream_t s);
+// out = beta * out + scale * sum of the n_src replicas.
 void reduce_replicas(const CommBufs& srcs, int n_src, void* out, long long n_elems, int is_fp32, float scale,
-                     cudaStream_t s);
+                     cudaStream_t s, float beta = 0.f);
 long long multi_copy_units(long long bytes);
 void multi_copy(const CopySeg* segs_dev, int n_segs, long long total_units, int max_blocks, cudaStream_t s);
 

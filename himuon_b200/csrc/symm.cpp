@@ -81,13 +81,15 @@ class Comm {
     allreduce_symm(peers_, b, n_elems, fp32 ? 1 : 0, static_cast<float>(scale), epoch_, static_cast<int>(max_blocks),
                    at::cuda::getCurrentCUDAStream().stream());
   }
-  // out = scale * sum over ranks of the heap region at offset_bytes.
-  void reduce_to(int64_t offset_bytes, at::Tensor out, double scale) {
+  // out = beta * out + scale * sum over ranks of the heap region at offset_bytes (out.numel() elements of out's dtype).
+  void reduce_to(int64_t offset_bytes, at::Tensor out, double scale, double beta) {
     TORCH_CHECK(out.is_cuda() && out.is_contiguous(), "himuon reduce_to: contiguous CUDA output expected");
+    TORCH_CHECK(offset_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0,
+                "himuon reduce_to: 16-byte aligned regions expected");
     CommBufs b{};
     for (int r = 0; r < peers_.world; ++r) b.ptr[r] = reinterpret_cast<char*>(heaps_[r]) + offset_bytes;
     reduce_replicas(b, peers_.world, out.data_ptr(), out.numel(), out.scalar_type() == at::kFloat ? 1 : 0,
-                    static_cast<float>(scale), at::cuda::getCurrentCUDAStream().stream());
+                    static_cast<float>(scale), at::cuda::getCurrentCUDAStream().stream(), static_cast<float>(beta));
   }
   void copy_segments(const at::Tensor& segs, int64_t n_segs, int64_t total_units, int64_t max_blocks) {
     TORCH_CHECK(segs.is_cuda() && segs.numel() >= n_segs * (int64_t)sizeof(CopySeg), "himuon copy_segments: table too small");
@@ -115,7 +117,7 @@ void bind_symm(py::module_& m) {
       .def_static("flag_bytes", &Comm::flag_bytes)
       .def("barrier", &Comm::barrier)
       .def("allreduce", &Comm::allreduce)
-      .def("reduce_to", &Comm::reduce_to)
+      .def("reduce_to", &Comm::reduce_to, py::arg("offset_bytes"), py::arg("out"), py::arg("scale"), py::arg("beta") = 0.0)
       .def("copy_segments", &Comm::copy_segments);
 }
 

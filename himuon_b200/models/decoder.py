@@ -179,11 +179,18 @@ class CausalLM(nn.Module):
         cos_sin = self._rope(S, input_ids.device)
         h = ops.embedding(input_ids, self.model.embed_tokens.weight).reshape(B * S, -1)
         delta = None
-        for layer in self.model.layers:
+        # a sharding engine that stages weights or gradients per layer group is told where the layer loop stands
+        engine = getattr(self, "_bank_engine", None)
+        fenced = engine is not None and getattr(engine, "uses_fences", False)
+        for i, layer in enumerate(self.model.layers):
+            if fenced:
+                h, delta = engine.pre_layer(i, h, delta)
             if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
                 h, delta = checkpoint(layer, h, delta, B, S, cos_sin, use_reentrant=False)
             else:
                 h, delta = layer(h, delta, B, S, cos_sin)
+            if fenced:
+                h, delta = engine.post_layer(i, h, delta)
         return ops.add_rmsnorm(h, delta, self.model.norm.weight, self.model.norm.variance_epsilon, defer_dw=True)[1]
 
     def forward(self, input_ids, attention_mask=None, labels=None, return_logits: bool = False, **_):

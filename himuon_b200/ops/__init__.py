@@ -129,10 +129,17 @@ class GradSink:
 
 class _LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, sink, param):
+    def forward(ctx, x, w, sink, param, w_getter=None):
         x2 = x.reshape(-1, x.shape[-1])
+        if w_getter is not None:
+            # The weight lives in a staging buffer that is reused for other layers between this forward and its
+            # backward: it is looked up again in backward instead of being saved (autograd would reject the reuse).
+            w = w_getter()
+            ctx.save_for_backward(x2)
+        else:
+            ctx.save_for_backward(x2, w)
         y = gemm(x2, w, trans_b=True)
-        ctx.save_for_backward(x2, w)
+        ctx.w_getter = w_getter
         ctx.sink = sink
         ctx.param = param
         ctx.x_shape = x.shape
@@ -140,7 +147,10 @@ class _LinearFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x2, w = ctx.saved_tensors
+        if ctx.w_getter is not None:
+            (x2,), w = ctx.saved_tensors, ctx.w_getter()
+        else:
+            x2, w = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
         if dy2.stride(-1) != 1 or dy2.stride(0) % 8 or dy2.data_ptr() % 16:
             dy2 = dy2.contiguous()            # column slices of a wider buffer are consumed in place
@@ -156,11 +166,18 @@ class _LinearFn(torch.autograd.Function):
                 gemm(dy2, x2, trans_a=True, out=p.grad, aux=p.grad, beta=1.0)
             else:
                 dw = gemm(dy2, x2, trans_a=True)
-        return dx, dw, None, None
+        return dx, dw, None, None, None
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, sink: GradSink | None = None) -> torch.Tensor:
-    """``x @ w.T``.  With ``sink`` the weight gradient is written there instead of returned."""
+def linear(x: torch.Tensor, w: torch.Tensor | None, sink: GradSink | None = None, w_getter=None) -> torch.Tensor:
+    """``x @ w.T``.  With ``sink`` the weight gradient is written there instead of returned.  ``w_getter`` (with a
+    sink): a callable returning the weight, called in forward and again in backward, for weights kept in a staging
+    buffer whose contents come and go between the two passes; ``w`` is then ignored."""
+    if w_getter is not None:
+        assert sink is not None, "a staged weight has no autograd gradient: a sink must take it"
+        if use_kernels(x) and x.dtype == torch.bfloat16:
+            return _LinearFn.apply(x, None, sink, None, w_getter)
+        return _SinkLinearRef.apply(x, None, sink, w_getter)
     if use_kernels(x) and w.dtype == torch.bfloat16:
         param = w if isinstance(w, torch.nn.Parameter) else None
         return _LinearFn.apply(x, w, sink, param)
@@ -173,14 +190,22 @@ class _SinkLinearRef(torch.autograd.Function):
     """CPU / fp32 counterpart of the sink path (used by the bank engine off-GPU)."""
 
     @staticmethod
-    def forward(ctx, x, w, sink):
-        ctx.save_for_backward(x, w)
+    def forward(ctx, x, w, sink, w_getter=None):
+        if w_getter is not None:
+            w = w_getter()
+            ctx.save_for_backward(x)
+        else:
+            ctx.save_for_backward(x, w)
+        ctx.w_getter = w_getter
         ctx.sink = sink
         return torch.nn.functional.linear(x, w)
 
     @staticmethod
     def backward(ctx, dy):
-        x, w = ctx.saved_tensors
+        if ctx.w_getter is not None:
+            (x,), w = ctx.saved_tensors, ctx.w_getter()
+        else:
+            x, w = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
         x2 = x.reshape(-1, x.shape[-1])
         dw = (dy2.float().t() @ x2.float()).to(ctx.sink.buffer.dtype)
@@ -189,7 +214,7 @@ class _SinkLinearRef(torch.autograd.Function):
             ctx.sink.mark_used()
         else:
             ctx.sink.buffer.add_(dw)
-        return (dy2 @ w).view(x.shape), None, None
+        return (dy2 @ w).view(x.shape), None, None, None
 
 
 # ------------------------------------------------------------------------------------------- deferred norm-weight grads

@@ -26,8 +26,9 @@ class AdamW(Optimizer):
         self._table = AdamTable()
 
     def _signature(self):
-        return tuple((p.data_ptr(), p.grad.data_ptr()) for g in self.param_groups for p in g["params"]
-                     if p.grad is not None)
+        # parameter, gradient and moment addresses: the device table is rebuilt when any of them moves
+        return tuple((p.data_ptr(), p.grad.data_ptr(), m.data_ptr() if torch.is_tensor(m := self.state[p].get("exp_avg")) else 0)
+                     for g in self.param_groups for p in g["params"] if p.grad is not None)
 
     def load_state_dict(self, state_dict):
         """Restores the state and drops the device entry table (it holds the addresses of the replaced moments)."""

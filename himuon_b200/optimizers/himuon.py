@@ -386,6 +386,12 @@ class HiMuon(Optimizer):
                 else:
                     sig.append(0)
                 sig.append(_local(p.data).data_ptr())
+                st = self.state.get(p)
+                if st:                                  # state tensors move when they are offloaded between steps
+                    for key in ("momentum_buffer", "moment1", "moment2"):
+                        v = st.get(key)
+                        if torch.is_tensor(v):
+                            sig.append(_local(v).data_ptr())
         return tuple(sig)
 
     def _build_exec(self, device):

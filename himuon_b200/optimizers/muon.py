@@ -95,8 +95,9 @@ class Muon(Optimizer):
             return
         if self._data(first).is_cuda:
             t = self._table
-            sig = tuple((self._data(p).data_ptr(), self._grad(p).data_ptr()) for _, g in groups for p in g["params"]
-                        if p.grad is not None)
+            sig = tuple((self._data(p).data_ptr(), self._grad(p).data_ptr(),
+                         m.data_ptr() if torch.is_tensor(m := self.state[p].get("moment1")) else 0)
+                        for _, g in groups for p in g["params"] if p.grad is not None)
             if t.sig != sig:
                 items = []
                 prior = 0

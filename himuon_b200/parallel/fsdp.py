@@ -1,28 +1,48 @@
 """Bank-sharded engine (the FSDP path).
 
-Same-shape per-layer projections are stacked into ``(n_padded, H, W)`` banks
-(:mod:`himuon_b200.fsdp_bank`) and sharded on the layer axis: rank ``r`` owns the contiguous slots
-``[r*N_local, (r+1)*N_local)`` of every bank, i.e. whole matrices, so the optimizer needs no
-collective (the reference's layout, ``src/himuon/fsdp_bank`` + ``train_fsdp.py:108-133``).
+Same-shape per-layer projections are stacked into ``(n, H, W)`` banks (:mod:`himuon_b200.fsdp_bank`) and sharded on
+the layer axis in whole matrices, so the optimizer needs no collective (the reference's layout,
+``src/himuon/fsdp_bank`` + ``train_fsdp.py:108-133``).  What this engine decides itself:
 
-What differs from the reference's FSDP2 execution:
+* **Placement is round-robin.**  Layer ``l`` of every bank lives on rank ``l % world`` (k|v and gate|up keep their two
+  slots together), at local position ``l // world``.  Consecutive layers therefore have different owners - a
+  per-layer fetch spreads over all NVLink ports instead of draining one GPU - and the zero pad slots that make the
+  layer count a multiple of the world size spread over the ranks too (36 layers on 8 ranks: four ranks own 5 real
+  matrices per bank and four own 4, instead of seven owning 5 and one owning 1).
+* **Weights: gathered copy or staging ring** (``weights=``).
 
-* **All-gather once per optimizer step, not per micro-step.**  180 GB of HBM hold a full bf16
-  working copy of every bank, refreshed after each optimizer step by one ``multi_copy`` launch that
-  pulls the peers' shards over NVLink; all accumulation micro-steps reuse it.
-* **Weight gradients go straight into a symmetric full-bank buffer** (the wgrad GEMM accumulates in
-  its epilogue), never through autograd's index-select backward.
-* **Reduce-scatter fused into the optimizer.**  The owner reads the ``world`` replicas of its slots
-  through peer pointers inside HiMuon's ``momentum_tile`` kernel (sum -> 1/world -> momentum -> tile
-  layout); other optimizers get a plain ``.grad`` from one ``reduce_replicas`` launch.
-* Embeddings, lm_head and norms stay replicated; their gradients share the fused all-reduce.
+  - ``"gathered"``: every rank keeps a full bf16 working copy of every bank, refreshed after each optimizer step by
+    one ``multi_copy`` launch that pulls the peers' shards over NVLink; accumulation micro-steps do no parameter
+    communication (180 GB of HBM hold the copy).
+  - ``"ring"``: no full copy.  Layers are taken in groups of ``world`` consecutive layers (one per owner); two
+    group-sized staging slots rotate.  While group ``g`` computes, a side stream copies group ``g+1`` (``g-1`` in
+    backward) from the owners' shards with the copy engines - no SM is taken from the GEMMs, and rank ``r`` visits
+    the owners in the order ``r+1, r+2, ...`` so that at any moment every owner serves exactly one reader.  Each
+    remote matrix crosses NVLink once per pass and is read by the GEMMs from local memory.  Per-rank weight memory is
+    ``1/world`` of the banks plus the two slots.
+  - ``"peer"``: no copy at all; the GEMMs' own TMA loads read the owner's shard through its peer mapping.
 
-On CPU (gloo) the same bookkeeping runs over ``torch.distributed`` collectives.
+* **Gradients: replicated or sharded accumulation** (``grads=``).
+
+  - ``"replicated"``: every rank accumulates its micro-batches in a full-bank buffer written by the weight-gradient
+    GEMMs' epilogues; the owner sums the ``world`` replicas once per step, inside HiMuon's ``momentum_tile`` kernel
+    through peer pointers (other optimizers: one ``reduce_replicas`` launch per bank).  This is what FSDP2 does under
+    gradient accumulation too (unsharded gradients accumulate locally, one reduce-scatter per optimizer step).
+  - ``"sharded"``: no full-bank buffer.  The weight gradients of one layer group land in a group-sized staging
+    buffer; when the backward pass leaves the group, every owner sums its layer over the ranks (peer loads) straight
+    into its own ``(n_local, H, W)`` accumulator.  Per-rank gradient memory is ``1/world`` of the banks plus one
+    group; the price is one reduce-scatter per group per micro-batch on the critical path.
+
+* Embeddings, lm_head and norms stay replicated; their gradients share one fused all-reduce per step.
+
+On CPU (gloo) the same bookkeeping runs over ``torch.distributed`` collectives, which keeps placement, ring rotation
+and the fences testable without a GPU.
 """
 
 from __future__ import annotations
 
 import struct
+import warnings
 from contextlib import contextmanager
 
 import torch
@@ -35,25 +55,53 @@ from .symm import SymmetricHeap, _world
 
 
 class _BankState:
-    __slots__ = ("spec", "n_local", "shard", "shard_off", "grad_full", "grad_off", "gathered", "param", "sinks",
-                 "pair_sinks", "peer_shards")
+    __slots__ = ("spec", "unit", "n_units", "n_local", "shard", "shard_off", "grad_full", "grad_off", "gathered",
+                 "param", "sinks", "pair_sinks", "peer_shards", "ring", "gring", "gring_off", "grad_shard")
+
+
+class _GroupFence(torch.autograd.Function):
+    """Identity on the residual stream ``(h, delta)`` at a layer-group boundary.  Its backward runs exactly when the
+    backward pass crosses the boundary, which is where the engine rotates the staging ring and reduces a finished
+    group's gradients."""
+
+    @staticmethod
+    def forward(ctx, engine, kind, group, h, delta):
+        ctx.engine, ctx.kind, ctx.group = engine, kind, group
+        ctx.set_materialize_grads(False)
+        if delta is None:
+            return h.view_as(h), None
+        return h.view_as(h), delta.view_as(delta)
+
+    @staticmethod
+    def backward(ctx, gh, gd):
+        ctx.engine._on_backward_boundary(ctx.kind, ctx.group)
+        return None, None, None, gh, gd
 
 
 class ShardedEngine:
     def __init__(self, model: nn.Module, use_banks: bool = True, cpu_offload: bool = False, timeout_s: float = 120.0,
-                 gather_blocks: int = 0, peer_weights: bool = False):
-        """``peer_weights``: keep no gathered copy of the banks; every projection's GEMM (forward and dgrad) reads
-        the weight tiles by TMA straight from the owner rank's shard over NVLink, so the all-gather is fused into the
-        GEMMs' operand loads.  Saves one full copy of the banks and the per-step re-gather at the price of fetching
-        the weights over NVLink in every micro-step; off by default (180 GB of HBM hold the copy)."""
+                 gather_blocks: int = 0, peer_weights: bool = False, weights: str | None = None,
+                 grads: str = "replicated"):
+        """``weights``: ``"gathered"`` (default), ``"ring"`` or ``"peer"`` (``peer_weights=True`` is the older spelling
+        of the last); ``grads``: ``"replicated"`` (default) or ``"sharded"``; see the module docstring.
+        ``cpu_offload``: keep the optimizer's state tensors in pinned host memory between steps (see
+        :class:`OptimizerStateOffload`; the reference's ``--cpu-offload``, ``train_fsdp.py:58,120``)."""
         self.model = model
         self.rank, self.world = _world()
-        self.cpu_offload = cpu_offload
+        self.cpu_offload = bool(cpu_offload)
         self.gather_blocks = gather_blocks
         first = next(model.parameters())
         self.device, self.dtype = first.device, first.dtype
         self.cuda = self.device.type == "cuda"
-        self.peer_weights = bool(peer_weights) and self.cuda and self.dtype == torch.bfloat16
+        weights = weights or ("peer" if peer_weights else "gathered")
+        if weights not in ("gathered", "ring", "peer") or grads not in ("replicated", "sharded"):
+            raise ValueError(f"ShardedEngine: unknown mode weights={weights!r} grads={grads!r}")
+        if weights == "peer" and not (self.cuda and self.dtype == torch.bfloat16):
+            weights = "gathered"                      # peer reads exist only in the TMA GEMMs
+        if self.world == 1:
+            weights, grads = "gathered", "replicated"   # one rank owns everything: the shard is the working copy
+        self.weights_mode, self.grads_mode = weights, grads
+        self.peer_weights = weights == "peer"
         esz = torch.empty((), dtype=self.dtype).element_size()
         self.banks = None
         bank_full = []
@@ -61,6 +109,8 @@ class ShardedEngine:
             scheme = Llama3BankScheme() if getattr(model.config, "model_type", "qwen3") == "llama" else Qwen3BankScheme()
             model, self.banks = wrap_with_banks(model, scheme, self.world)
             bank_full = [(b, getattr(model, b.spec.name)) for b in self.banks]
+        self.n_layers = max((b.spec.n_logical // self._unit_of(b.spec) for b, _ in bank_full), default=0)
+        self.n_groups = -(-self.n_layers // self.world) if self.n_layers else 0
         self._pad = 16 * max(1, self.world)
         replicated = [p for n, p in model.named_parameters() if p.requires_grad
                       and (self.banks is None or n not in {b.spec.name for b in self.banks})]
@@ -71,7 +121,11 @@ class ShardedEngine:
                    for dt, ps in rep_by_dtype.items())
         for b, full in bank_full:
             H, W = b.spec.matrix_shape
-            need += (b.spec.n_padded // self.world + b.spec.n_padded) * H * W * esz + 8192
+            unit = self._unit_of(b.spec)
+            n_local = unit * self.n_groups
+            slots = n_local                                            # the owned shard
+            slots += n_local * self.world if grads == "replicated" else unit * self.world   # gradient buffer
+            need += slots * H * W * esz + 16384
         self.heap = SymmetricHeap(need, self.device, timeout_s)
 
         # ---- replicated parameters: gradients in one flat symmetric region per dtype
@@ -88,45 +142,65 @@ class ShardedEngine:
                 cursor += p.numel()
             self.regions.append((flat, offset))
 
-        # ---- banks: owned shard + full-bank gradient buffer in the heap, gathered working copy outside it
+        # ---- banks
         self.state: dict[str, _BankState] = {}
         for b, full in bank_full:
             st = _BankState()
             st.spec = b.spec
             H, W = b.spec.matrix_shape
-            n_pad = b.spec.n_padded
-            st.n_local = n_pad // self.world
+            st.unit = self._unit_of(b.spec)
+            st.n_units = b.spec.n_logical // st.unit
+            st.n_local = st.unit * self.n_groups
+            n_phys = st.n_local * self.world
             if self.world > 1:
                 dist.broadcast(full.data, src=0)
             st.shard, st.shard_off = self.heap.alloc((st.n_local, H, W), self.dtype)
-            st.shard.copy_(full.data[self.rank * st.n_local:(self.rank + 1) * st.n_local])
-            st.grad_full, st.grad_off = self.heap.alloc((n_pad, H, W), self.dtype)
-            st.grad_full.zero_()
-            st.peer_shards = None
+            st.shard.zero_()
+            for s in range(b.spec.n_logical):
+                owner, loc = self._place(st, s)
+                if owner == self.rank:
+                    st.shard[loc].copy_(full.data[s])
+            st.grad_full = st.gring = st.grad_shard = None
+            st.grad_off = st.gring_off = 0
+            if grads == "replicated":
+                st.grad_full, st.grad_off = self.heap.alloc((n_phys, H, W), self.dtype)
+                st.grad_full.zero_()
+            else:
+                st.gring, st.gring_off = self.heap.alloc((st.unit * self.world, H, W), self.dtype)
+                st.gring.zero_()
+                st.grad_shard = torch.zeros(st.n_local, H, W, device=self.device, dtype=self.dtype)
+            st.peer_shards = st.gathered = st.ring = None
             if self.world == 1:
                 st.gathered = st.shard
-            elif self.peer_weights and st.n_local % 2 == 0:       # an even shard: no k|v or gate|up pair straddles ranks
-                st.gathered = None
+            elif weights == "peer":
                 st.peer_shards = [st.shard if r == self.rank else
                                   self.heap.view(r, st.shard_off, (st.n_local, H, W), self.dtype)
                                   for r in range(self.world)]
+            elif weights == "ring":
+                st.ring = [torch.empty(st.unit * self.world, H, W, device=self.device, dtype=self.dtype) for _ in range(2)]
+                if self.cuda:
+                    st.peer_shards = [st.shard if r == self.rank else
+                                      self.heap.view(r, st.shard_off, (st.n_local, H, W), self.dtype)
+                                      for r in range(self.world)]
             else:
-                st.gathered = torch.empty(n_pad, H, W, device=self.device, dtype=self.dtype)
-                st.gathered.copy_(full.data)
+                st.gathered = torch.zeros(n_phys, H, W, device=self.device, dtype=self.dtype)
+                for s in range(b.spec.n_logical):
+                    st.gathered[self._phys(st, s)].copy_(full.data[s])
             param = nn.Parameter(st.shard, requires_grad=True)
             param._bank_spec = b.spec
-            lo = self.rank * st.n_local
-            param._hm_skip_slots = {i for i in range(st.n_local) if lo + i >= b.spec.n_logical}
-            if self.cuda:
-                slice_off = st.grad_off + lo * H * W * esz
+            # pad slots (layers past the model's depth) hold zeros and need no optimizer work
+            param._hm_skip_slots = {lu * st.unit + k for lu in range(self.n_groups) for k in range(st.unit)
+                                    if lu * self.world + self.rank >= st.n_units}
+            if self.cuda and grads == "replicated":
+                slice_off = st.grad_off + self.rank * st.n_local * H * W * esz
                 param._hm_grad_sources = [self.heap.view(r, slice_off, (st.n_local, H, W), self.dtype)
                                           for r in range(self.world)]
                 param._hm_grad_scale = 1.0 / self.world
+            if grads == "sharded":
+                param.grad = st.grad_shard
             setattr(model, b.spec.name, param)
             st.param = param
-            st.sinks = [ops.GradSink(st.grad_full[i]) for i in range(n_pad)]
-            # neighbouring slots (k|v, gate|up) viewed as one (2H, W) matrix for the fused pair GEMMs
-            st.pair_sinks = {i: ops.GradSink(st.grad_full[i:i + 2].view(2 * H, W)) for i in range(0, n_pad - 1, 2)}
+            self._make_sinks(st)
             self.state[b.spec.name] = st
             b.parameter = None            # the un-sharded original is released
         del bank_full
@@ -135,42 +209,241 @@ class ShardedEngine:
         object.__setattr__(model, "_bank_engine", self if self.banks is not None else None)
         self.materialize_grads = False    # True: produce .grad for bank shards (optimizers without the fused path)
         self._copy_table = None
+        self._offload = None
+        # staging-ring bookkeeping (host side; it describes the work enqueued so far, in program order)
+        self._slot_group = [None, None]
+        self._slot_ready = [None, None]
+        self._copy_stream = torch.cuda.Stream(self.device) if (self.cuda and weights == "ring") else None
+        self.ring_fetches = 0             # groups copied so far (tests, diagnostics)
+        self.group_reductions = 0
         if self.world > 1:
             self.heap.barrier()
+
+    # ------------------------------------------------------------------ placement
+    @staticmethod
+    def _unit_of(spec) -> int:
+        """Slots per layer: 2 for the interleaved k|v and gate|up banks, 1 otherwise."""
+        return 2 if spec.name in ("kv_bank", "gate_up_bank") else 1
+
+    def _place(self, st: _BankState, slot: int) -> tuple[int, int]:
+        """Bank slot (the index ``rewire_linear`` recorded) -> (owner rank, index in the owner's shard)."""
+        u, k = divmod(slot, st.unit)
+        return u % self.world, (u // self.world) * st.unit + k
+
+    def _phys(self, st: _BankState, slot: int) -> int:
+        """Position of a bank slot in the owner-major full-size buffers (gathered copy, replicated gradients)."""
+        owner, loc = self._place(st, slot)
+        return owner * st.n_local + loc
+
+    def _ring_pos(self, st: _BankState, slot: int) -> tuple[int, int]:
+        """Bank slot -> (layer group, index in a group-sized staging buffer)."""
+        u, k = divmod(slot, st.unit)
+        return u // self.world, (u % self.world) * st.unit + k
+
+    def _make_sinks(self, st: _BankState):
+        H, W = st.spec.matrix_shape
+        n = st.spec.n_logical
+        if st.grad_full is not None:
+            st.sinks = [ops.GradSink(st.grad_full[self._phys(st, s)]) for s in range(n)]
+            st.pair_sinks = {s: ops.GradSink(st.grad_full[self._phys(st, s):self._phys(st, s) + 2].view(2 * H, W))
+                             for s in range(0, n - 1, 2)} if st.unit == 2 else {}
+        else:
+            st.sinks = [ops.GradSink(st.gring[self._ring_pos(st, s)[1]]) for s in range(n)]
+            st.pair_sinks = {s: ops.GradSink(st.gring[self._ring_pos(st, s)[1]:self._ring_pos(st, s)[1] + 2].view(2 * H, W))
+                             for s in range(0, n - 1, 2)} if st.unit == 2 else {}
 
     def _padded(self, n: int) -> int:
         return -(-n // self._pad) * self._pad
 
+    def bank_bytes(self) -> dict:
+        """Bytes this rank holds for bank weights and bank gradients, and the size of the whole (unsharded) banks
+        without and with the pad layers that make the layer count a multiple of the world size."""
+        esz = torch.empty((), dtype=self.dtype).element_size()
+        w = g = total = padded = 0
+        for st in self.state.values():
+            H, W = st.spec.matrix_shape
+            m = H * W * esz
+            total += st.spec.n_logical * m
+            padded += st.n_local * self.world * m
+            w += st.n_local * m
+            if st.gathered is not None and st.gathered is not st.shard:
+                w += st.gathered.shape[0] * m
+            if st.ring is not None:
+                w += sum(r.shape[0] for r in st.ring) * m
+            if st.grad_full is not None:
+                g += st.grad_full.shape[0] * m
+            if st.gring is not None:
+                g += (st.gring.shape[0] + st.grad_shard.shape[0]) * m
+        return {"weights": w, "grads": g, "banks_total": total, "banks_padded": padded}
+
     # ------------------------------------------------------------------ optimizer hookup
     def attach_optimizer(self, optimizer):
-        """HiMuon reads the gradient replicas itself (fused reduce-scatter); any other optimizer gets a
-        reduced ``.grad`` on the bank shards."""
+        """HiMuon reads the gradient replicas itself (fused reduce-scatter); any other optimizer gets a reduced
+        ``.grad`` on the bank shards.  With ``cpu_offload`` the optimizer's ``step`` is wrapped so that its state
+        lives in pinned host memory between steps."""
         from ..optimizers import HiMuon
-        self.materialize_grads = not (isinstance(optimizer, HiMuon) and self.cuda)
-        if self.materialize_grads:
+        fused = isinstance(optimizer, HiMuon) and self.cuda and self.grads_mode == "replicated"
+        self.materialize_grads = not fused and self.grads_mode == "replicated"
+        if not fused:
             for st in self.state.values():
                 if hasattr(st.param, "_hm_grad_sources"):
                     del st.param._hm_grad_sources
+        if self.cpu_offload and self.cuda:
+            self._offload = OptimizerStateOffload(optimizer)
+        return optimizer
 
     # ------------------------------------------------------------------ forward / backward plumbing
     def _weights(self, st: _BankState, idx: int, n: int) -> torch.Tensor:
-        """Slots ``idx .. idx+n`` as an ``(n, H, W)`` tensor: the gathered copy, or the owner's shard seen through
-        its peer mapping (only this package's own TMA GEMMs ever read that memory)."""
+        """Bank slots ``idx .. idx+n`` as an ``(n, H, W)`` tensor from wherever this mode keeps them: the gathered
+        copy, the owner's shard (own layers; or, in peer mode, seen through the peer mapping, which only this
+        package's own TMA GEMMs ever read) or the staging slot of the layer's group."""
         if st.gathered is not None:
-            return st.gathered[idx:idx + n]
-        r, j = divmod(idx, st.n_local)
-        return st.peer_shards[r][j:j + n]
+            p = self._phys(st, idx)
+            return st.gathered[p:p + n]
+        owner, loc = self._place(st, idx)
+        if st.ring is None:
+            return st.peer_shards[owner][loc:loc + n]
+        if owner == self.rank:
+            return st.shard[loc:loc + n]
+        g, pos = self._ring_pos(st, idx)
+        if self._slot_group[g % 2] != g:
+            self._acquire(g)                         # a caller outside the layer loop (or the fences are not in use)
+        return st.ring[g % 2][pos:pos + n]
 
     def linear(self, x, bank_name: str, idx: int, bias=None):
         st = self.state[bank_name]
-        y = ops.linear(x, self._weights(st, idx, 1)[0], sink=st.sinks[idx])
+        if st.ring is not None:          # staged weights are looked up again in backward, not saved by autograd
+            y = ops.linear(x, None, sink=st.sinks[idx], w_getter=lambda: self._weights(st, idx, 1)[0])
+        else:
+            y = ops.linear(x, self._weights(st, idx, 1)[0], sink=st.sinks[idx])
         return y if bias is None else y + bias
 
     def linear_pair(self, x, bank_name: str, idx: int):
         """Slots ``idx`` and ``idx+1`` applied as one ``(2H, W)`` projection (one GEMM in each direction)."""
         st = self.state[bank_name]
         H, W = st.spec.matrix_shape
+        if st.ring is not None:
+            return ops.linear(x, None, sink=st.pair_sinks[idx],
+                              w_getter=lambda: self._weights(st, idx, 2).view(2 * H, W))
         return ops.linear(x, self._weights(st, idx, 2).view(2 * H, W), sink=st.pair_sinks[idx])
+
+    # ---- layer-group fences (called by the decoder's layer loop)
+    @property
+    def uses_fences(self) -> bool:
+        return self.banks is not None and self.world > 1 and (self.weights_mode == "ring" or self.grads_mode == "sharded")
+
+    def pre_layer(self, i: int, h, delta):
+        """Before decoder layer ``i``: at the first layer of a group make the group's weights available and start
+        fetching the next group."""
+        if not self.uses_fences or i % self.world:
+            return h, delta
+        g = i // self.world
+        if i == 0:
+            self._begin_pass()
+        if self.weights_mode == "ring":
+            self._acquire(g)
+            if g + 1 < self.n_groups:
+                self._prefetch(g + 1)
+        if torch.is_grad_enabled() and h.requires_grad:
+            h, delta = _GroupFence.apply(self, "start", g, h, delta)
+        return h, delta
+
+    def post_layer(self, i: int, h, delta):
+        """After decoder layer ``i``: the last layer of a group closes it (the backward pass enters the group here)."""
+        if not self.uses_fences or ((i + 1) % self.world and i + 1 != self.n_layers):
+            return h, delta
+        if torch.is_grad_enabled() and h.requires_grad:
+            h, delta = _GroupFence.apply(self, "end", i // self.world, h, delta)
+        return h, delta
+
+    def _begin_pass(self):
+        """A new forward pass: nothing is assumed about what the staging slots hold (the optimizer may have stepped),
+        and every group-staged gradient sink starts by overwriting."""
+        self._slot_group = [None, None]
+        self._slot_ready = [None, None]
+        if self.grads_mode == "sharded":
+            for st in self.state.values():
+                for s in st.sinks:
+                    s.reset()
+                for s in st.pair_sinks.values():
+                    s.reset()
+
+    def _on_backward_boundary(self, kind: str, g: int):
+        if kind == "end":                              # the backward pass is about to run group g's layers
+            if self.weights_mode == "ring":
+                self._acquire(g)
+                if g > 0:
+                    self._prefetch(g - 1)
+        else:                                          # group g's layers are done
+            if self.grads_mode == "sharded":
+                self._reduce_group(g)
+
+    def _prefetch(self, g: int):
+        """Start copying layer group ``g`` into its staging slot.  The copies are ordered after everything enqueued on
+        the compute stream so far (the slot's previous group is no longer needed at this point of the layer loop)."""
+        slot = g % 2
+        if self._slot_group[slot] == g:
+            return
+        self._slot_group[slot] = g
+        self.ring_fetches += 1
+        if not self.cuda:
+            for st in self.state.values():
+                dist.all_gather_into_tensor(st.ring[slot], st.shard[g * st.unit:(g + 1) * st.unit].contiguous())
+            self._slot_ready[slot] = None
+            return
+        main = torch.cuda.current_stream(self.device)
+        free = torch.cuda.Event()
+        free.record(main)
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(free)
+            # owners in the order rank+1, rank+2, ...: at any moment every owner is read by exactly one rank
+            for j in range(1, self.world):
+                owner = (self.rank + j) % self.world
+                for st in self.state.values():
+                    dst = st.ring[slot][owner * st.unit:(owner + 1) * st.unit]
+                    dst.copy_(st.peer_shards[owner][g * st.unit:(g + 1) * st.unit], non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(self._copy_stream)
+        self._slot_ready[slot] = ready
+
+    def _acquire(self, g: int):
+        """Make the compute stream wait until layer group ``g`` sits in its staging slot (fetching it now if no
+        prefetch is under way)."""
+        slot = g % 2
+        if self._slot_group[slot] != g:
+            self._prefetch(g)
+        ready = self._slot_ready[slot]
+        if ready is not None:
+            torch.cuda.current_stream(self.device).wait_event(ready)
+            self._slot_ready[slot] = None
+
+    def _reduce_group(self, g: int):
+        """Sharded gradients: add this micro-batch's gradients of layer group ``g``, summed over the ranks, to the
+        owners' accumulators.  Every rank owns one layer of the group, so this is a reduce-scatter; the barriers
+        before and after make the peers' staging buffers complete before they are read and free before the next
+        group overwrites them."""
+        self.group_reductions += 1
+        scale = 1.0 / self.world
+        if not self.cuda:
+            for st in self.state.values():
+                work = st.gring.float()
+                dist.all_reduce(work)
+                if g * self.world + self.rank < st.n_units:
+                    mine = work[self.rank * st.unit:(self.rank + 1) * st.unit] * scale
+                    st.grad_shard[g * st.unit:(g + 1) * st.unit].add_(mine.to(self.dtype))
+            return
+        self.heap.barrier()
+        ops._count()
+        for st in self.state.values():
+            if g * self.world + self.rank >= st.n_units:
+                continue                               # this rank's slot of the group is a pad layer
+            H, W = st.spec.matrix_shape
+            esz = st.shard.element_size()
+            off = st.gring_off + self.rank * st.unit * H * W * esz
+            self.heap.comm.reduce_to(off, st.grad_shard[g * st.unit:(g + 1) * st.unit], scale, 1.0)
+            ops._count()
+        self.heap.barrier()
+        ops._count()
 
     @contextmanager
     def no_sync(self):
@@ -196,7 +469,7 @@ class ShardedEngine:
                 st.param.grad = torch.empty_like(st.shard)
             if self.cuda:
                 esz = st.shard.element_size()
-                self.heap.comm.reduce_to(st.grad_off + lo * H * W * esz, st.param.grad, 1.0 / self.world)
+                self.heap.comm.reduce_to(st.grad_off + lo * H * W * esz, st.param.grad, 1.0 / self.world, 0.0)
                 ops._count()
             else:
                 work = st.grad_full.float()
@@ -215,16 +488,20 @@ class ShardedEngine:
                 s.reset()
             for s in st.pair_sinks.values():
                 s.reset()
+            if st.grad_shard is not None:
+                st.grad_shard.zero_()
             if self.materialize_grads and set_to_none and self.world > 1:
                 st.param.grad = None
+        self._slot_group = [None, None]            # the shards changed: staged copies are stale
+        self._slot_ready = [None, None]
 
     def _regather(self):
+        if all(st.gathered is None for st in self.state.values()):
+            return                                   # ring / peer modes keep no gathered copy
         if not self.cuda:
             for st in self.state.values():
                 dist.all_gather_into_tensor(st.gathered, st.shard.contiguous())
             return
-        if all(st.gathered is None for st in self.state.values()):
-            return                                   # every bank is read in place through the peer mappings
         if self._copy_table is None:
             ext = self.heap._ext
             tab, units, n = bytearray(), 0, 0
@@ -246,25 +523,37 @@ class ShardedEngine:
 
     # ------------------------------------------------------------------ checkpoints
     def full_state_dict(self) -> dict:
-        """Full, un-banked state dict with the Hugging Face ``model.layers.{i}.*`` keys (every rank holds the
-        gathered banks, so no communication is needed; the reference gathers to rank 0, ``train_fsdp.py:285-297``)."""
+        """Full, un-banked state dict with the Hugging Face ``model.layers.{i}.*`` keys on rank 0 (``{}`` on the other
+        ranks, which do not write; the reference gathers to rank 0 the same way, ``train_fsdp.py:285-297``).  The
+        banks are gathered one at a time from the owners' shards."""
         sd = {}
         bank_names = set(self.state)
-        for k, v in self.model.state_dict().items():
-            if k not in bank_names:
-                sd[k] = v.detach().cpu()
+        if self.rank == 0:
+            for k, v in self.model.state_dict().items():
+                if k not in bank_names:
+                    sd[k] = v.detach().cpu()
         if self.banks is None:
             return sd
         for name, st in self.state.items():
-            if st.gathered is not None:
-                sd[name] = st.gathered.detach().cpu()
+            if self.world > 1:
+                full = torch.empty(st.n_local * self.world, *st.spec.matrix_shape, device=self.device, dtype=self.dtype)
+                dist.all_gather_into_tensor(full, st.shard.detach().contiguous())
             else:
-                full = torch.empty(st.spec.n_padded, *st.spec.matrix_shape, device=self.device, dtype=self.dtype)
-                dist.all_gather_into_tensor(full, st.shard.detach().contiguous())   # every rank sends its own shard
-                sd[name] = full.cpu()
-        return unbank_state_dict(sd, self.banks)
+                full = st.shard.detach()
+            if self.rank == 0:
+                order = torch.tensor([self._phys(st, s) for s in range(st.spec.n_logical)], device=full.device)
+                canon = full.index_select(0, order).cpu()
+                pad = st.spec.n_padded - canon.shape[0]
+                if pad > 0:
+                    canon = torch.cat([canon, canon.new_zeros(pad, *canon.shape[1:])], 0)
+                sd[name] = canon
+            del full
+        return unbank_state_dict(sd, self.banks) if self.rank == 0 else {}
 
     def close(self):
+        if self._offload is not None:
+            self._offload.restore()
+            self._offload = None
         for p in self.model.parameters():
             p.grad = None
             if hasattr(p, "_hm_grad_sources"):
@@ -273,3 +562,58 @@ class ShardedEngine:
         self.regions = []
         self._copy_table = None
         self.heap.close()
+
+
+class OptimizerStateOffload:
+    """Keeps an optimizer's state tensors (momentum, Adam moments) in pinned host memory between steps.
+
+    ``step()`` is wrapped: the state is copied to the device right before it and back to the host right after, both
+    asynchronously on the compute stream, and the device copies are released in between, so the forward and backward
+    passes have that memory for activations.  This is the part of FSDP2's ``CPUOffloadPolicy``
+    (``train_fsdp.py:58,120``) that matters on a 180 GB device; parameters and gradients stay in HBM because every
+    GEMM needs them.  Device addresses of the state change from step to step, so CUDA-graph capture of the optimizer
+    is switched off and the optimizers' device tables are rebuilt when they notice the change.
+    """
+
+    def __init__(self, optimizer):
+        self.optimizer = optimizer
+        self._host: dict[tuple, torch.Tensor] = {}
+        if getattr(optimizer, "_cuda_graph_enabled", False):
+            warnings.warn("cpu_offload: CUDA-graph capture of the optimizer step is disabled (state addresses change)")
+            optimizer._cuda_graph_enabled = False
+            if hasattr(optimizer, "_invalidate_plan_cache"):
+                optimizer._invalidate_plan_cache()
+        self._inner_step = optimizer.step
+        optimizer.step = self._step
+        self.bytes_offloaded = 0
+
+    def _step(self, *a, **k):
+        self._load()
+        out = self._inner_step(*a, **k)
+        self._store()
+        return out
+
+    def _load(self):
+        for p, st in self.optimizer.state.items():
+            for key, v in list(st.items()):
+                if torch.is_tensor(v) and v.device.type == "cpu" and (id(p), key) in self._host:
+                    st[key] = v.to(p.device, non_blocking=True)
+
+    def _store(self):
+        total = 0
+        for p, st in self.optimizer.state.items():
+            for key, v in list(st.items()):
+                if torch.is_tensor(v) and v.is_cuda and v.numel() > 1:
+                    host = self._host.get((id(p), key))
+                    if host is None or host.shape != v.shape or host.dtype != v.dtype:
+                        host = torch.empty(v.shape, dtype=v.dtype, pin_memory=True)
+                        self._host[(id(p), key)] = host
+                    host.copy_(v, non_blocking=True)
+                    st[key] = host
+                    total += v.numel() * v.element_size()
+        self.bytes_offloaded = total
+
+    def restore(self):
+        """Bring the state back to the device and unwrap ``step`` (before a state-dict save, or at shutdown)."""
+        self._load()
+        self.optimizer.step = self._inner_step

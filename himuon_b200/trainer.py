@@ -73,9 +73,18 @@ def build_arg_parser(mode: str) -> argparse.ArgumentParser:
     if mode == "fsdp":
         p.add_argument("--num-decay-steps", type=int, default=400)
         p.add_argument("--min-lr-ratio", type=float, default=0.1)
-        p.add_argument("--cpu-offload", action="store_true")
+        p.add_argument("--cpu-offload", action="store_true",
+                       help="keep the optimizer state in pinned host memory between steps")
+        p.add_argument("--fsdp-weights", dest="fsdp_weights", type=str, default="gathered",
+                       choices=["gathered", "ring", "peer"],
+                       help="working copy of the parameter banks: a full gathered copy refreshed once per step, a "
+                            "two-slot staging ring of layer groups fetched from the owners during forward/backward, or "
+                            "none (the GEMMs read the owner's shard over NVLink)")
+        p.add_argument("--fsdp-grads", dest="fsdp_grads", type=str, default="replicated", choices=["replicated", "sharded"],
+                       help="gradient accumulation: full-bank buffer per rank reduced once per step, or per-layer-group "
+                            "reduce-scatter onto the owner's shard-sized accumulator")
         p.add_argument("--peer-weights", dest="peer_weights", action="store_true",
-                       help="keep no gathered copy of the banks; the GEMMs read weight tiles from the owner rank over NVLink")
+                       help="same as --fsdp-weights peer")
     return p
 
 
@@ -358,9 +367,16 @@ def run_training(args, mode: str) -> dict:
         engine = DataParallelEngine(model)
     elif mode == "fsdp":
         from .parallel.fsdp import ShardedEngine
-        engine = ShardedEngine(model, use_banks=args.optimizer.lower() in ("himuon", "muon-fsdp"),
-                               cpu_offload=getattr(args, "cpu_offload", False),
-                               peer_weights=getattr(args, "peer_weights", False))
+        # Banks (whole matrices sharded on the layer axis) serve every optimizer that updates a stacked (n, H, W)
+        # parameter correctly: himuon, muon-fsdp, and adamw, which is element-wise.  The others (muon, himuon-legacy,
+        # soap) need one 2-D parameter per matrix and run replicated.
+        opt_name = args.optimizer.lower()
+        use_banks = opt_name in ("himuon", "muon-fsdp", "adamw")
+        if not use_banks:
+            log(f"optimizer {opt_name!r} needs per-matrix parameters: parameters are replicated, not sharded")
+        weights = "peer" if getattr(args, "peer_weights", False) else getattr(args, "fsdp_weights", "gathered")
+        engine = ShardedEngine(model, use_banks=use_banks, cpu_offload=getattr(args, "cpu_offload", False),
+                               weights=weights, grads=getattr(args, "fsdp_grads", "replicated"))
         banks = engine.banks
 
     tokens_per_step = args.batch_size * args.max_length * args.gradient_accumulation_steps * world_size

@@ -33,10 +33,26 @@ def scenario_train(mode, optimizer_name):
 
     rank, world = dist.get_rank(), dist.get_world_size()
     torch.manual_seed(0)
-    model = CausalLM(_cfg())
+    # "fsdp:<weights>:<grads>[:ckpt]" selects the engine's staging modes; 5 layers on 2 ranks give 3 layer groups, the last
+    # one half empty, so the ring rotates and a pad layer takes part
+    mode, *opts = mode.split(":")
+    layers = 5 if opts else 3
+    model = CausalLM(_cfg(layers))
+    if "ckpt" in opts:
+        model.gradient_checkpointing_enable()
     if mode == "fsdp":
         from himuon_b200.parallel.fsdp import ShardedEngine
-        engine = ShardedEngine(model, use_banks=True)
+        engine = ShardedEngine(model, use_banks=True, weights=opts[0] if opts else None,
+                               grads=opts[1] if len(opts) > 1 else "replicated")
+        if opts and world > 1:
+            assert engine.weights_mode == opts[0] and engine.grads_mode == opts[1] and engine.uses_fences
+            b = engine.bank_bytes()
+            # this rank holds its 1/world share plus the staging slots, not the whole banks
+            groups = engine.n_groups
+            if opts[0] == "ring":
+                assert b["weights"] <= (1.0 / world + 2.0 / groups) * b["banks_padded"] + 1, b
+            if opts[1] == "sharded":
+                assert b["grads"] <= (1.0 / world + 1.0 / groups) * b["banks_padded"] + 1, b
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
         engine = DataParallelEngine(model)
@@ -49,9 +65,15 @@ def scenario_train(mode, optimizer_name):
     all_losses = [None] * world
     dist.all_gather_object(all_losses, losses)
     sd = engine.full_state_dict() if mode == "fsdp" else {k: v.detach().clone() for k, v in model.state_dict().items()}
+    if mode == "fsdp" and opts and world > 1:
+        groups = engine.n_groups
+        if opts[0] == "ring":          # every pass of every micro-batch walks all groups through the two slots
+            assert engine.ring_fetches >= 3 * 2 * groups, engine.ring_fetches
+        if opts[1] == "sharded":
+            assert engine.group_reductions == 3 * 2 * groups, engine.group_reductions
     if rank == 0:
         torch.manual_seed(0)
-        ref_model = CausalLM(_cfg())
+        ref_model = CausalLM(_cfg(layers))
         ref_opt = get_optimizer(optimizer_name if optimizer_name != "muon-fsdp" else "muon", ref_model, ns)
         per_rank = [_batches(r, world, 3, 2) for r in range(world)]
         ref_losses = []

@@ -10,10 +10,10 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def _cfg():
+def _cfg(layers=3):
     from himuon_b200.models import DecoderConfig
 
-    return DecoderConfig(model_type="qwen3", vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=3,
+    return DecoderConfig(model_type="qwen3", vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=layers,
                          num_attention_heads=4, num_key_value_heads=2, head_dim=128, tie_word_embeddings=True,
                          max_position_embeddings=512)
 
@@ -68,13 +68,29 @@ def scenario_train(mode, optimizer_name, device):
 
     rank, world = dist.get_rank(), dist.get_world_size()
     torch.manual_seed(0)
-    model = CausalLM(_cfg()).to(device, torch.bfloat16)
+    # "fsdp:<weights>:<grads>[:graph][:ckpt]": staging modes of the sharded engine, optionally with forward+backward
+    # replayed from CUDA graphs and with activation checkpointing; 5 layers on 2 ranks are 3 layer groups (the last
+    # half empty), so the ring rotates and a pad layer takes part
+    mode, *opts = mode.split(":")
+    layers = 5 if opts else 3
+    model = CausalLM(_cfg(layers)).to(device, torch.bfloat16)
+    if "ckpt" in opts:
+        model.gradient_checkpointing_enable()
     if mode in ("fsdp", "fsdp-peer"):
         from himuon_b200.parallel.fsdp import ShardedEngine
         # "fsdp-peer": no gathered copy; the GEMMs read the weights from the owner rank's shard over NVLink
-        engine = ShardedEngine(model, use_banks=True, timeout_s=30.0, peer_weights=(mode == "fsdp-peer"))
+        engine = ShardedEngine(model, use_banks=True, timeout_s=30.0, peer_weights=(mode == "fsdp-peer"),
+                               weights=opts[0] if opts else None, grads=opts[1] if len(opts) > 1 else "replicated")
         if mode == "fsdp-peer":
             assert any(st.gathered is None for st in engine.state.values()) or world == 1
+        if opts and world > 1:
+            assert engine.weights_mode == opts[0] and engine.grads_mode == opts[1] and engine.uses_fences
+            b, groups = engine.bank_bytes(), engine.n_groups
+            # per-rank bytes: the 1/world share plus the staging slots, not the whole banks
+            if opts[0] == "ring":
+                assert b["weights"] <= (1.0 / world + 2.0 / groups) * b["banks_padded"] + 1, b
+            if opts[1] == "sharded":
+                assert b["grads"] <= (1.0 / world + 1.0 / groups) * b["banks_padded"] + 1, b
         mode = "fsdp"
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
@@ -84,7 +100,8 @@ def scenario_train(mode, optimizer_name, device):
     opt = get_optimizer(optimizer_name, model, ns)
     if mode == "fsdp":
         engine.attach_optimizer(opt)
-    trainer = Trainer(model, opt, None, engine, grad_acc=2, device=device)
+    trainer = Trainer(model, opt, None, engine, grad_acc=2, device=device, graph_microbatch="graph" in opts,
+                      graph_warmup_steps=1)
     trainer.zero_set_to_none = False
     steps = 4
     losses = [float(trainer.train_step(b)) for b in _batches(rank, steps, 2, device)]
@@ -93,9 +110,11 @@ def scenario_train(mode, optimizer_name, device):
     all_losses = [None] * world
     dist.all_gather_object(all_losses, losses)
     sd = engine.full_state_dict() if mode == "fsdp" else {k: v.detach().cpu() for k, v in model.state_dict().items()}
+    if "graph" in opts:
+        assert set(trainer._mb_graphs) == {True, False}, "the micro-batch graphs were not captured"
     if rank == 0:
         torch.manual_seed(0)
-        ref_model = CausalLM(_cfg()).to(device, torch.bfloat16)
+        ref_model = CausalLM(_cfg(layers)).to(device, torch.bfloat16)
         ns_ref = argparse.Namespace(lr=lr, weight_decay=0.1, tile_size=128, cuda_graph=False)
         ref_opt = get_optimizer("muon" if optimizer_name == "muon-fsdp" else optimizer_name, ref_model, ns_ref)
         per_rank = [_batches(r, steps, 2, device) for r in range(world)]

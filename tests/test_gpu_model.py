@@ -200,3 +200,48 @@ def test_evaluate_between_train_steps_does_not_touch_gradients_on_the_kernel_pat
         c = _cos(p0[n], p1[n]).item()
         assert c > 0.99999, (n, c)
     ops.check_status()
+
+
+@pytest.mark.parametrize("opt_name", ["himuon", "adamw"])
+def test_cpu_offload_keeps_optimizer_state_on_the_host_between_steps(opt_name):
+    """--cpu-offload: momentum and Adam moments sit in pinned host memory while forward/backward run, come back for
+    the optimizer step, and training matches the run without offloading."""
+    from himuon_b200.models import CausalLM
+    from himuon_b200.optim import get_optimizer
+    from himuon_b200.parallel.fsdp import ShardedEngine
+    from himuon_b200.trainer import Trainer
+
+    def run(offload):
+        torch.manual_seed(0)
+        model = CausalLM(_small_cfg("qwen3")).cuda().bfloat16()
+        engine = ShardedEngine(model, use_banks=True, cpu_offload=offload)
+        ns = argparse.Namespace(lr=1e-2 if opt_name == "himuon" else 1e-3, weight_decay=0.1, tile_size=128,
+                                cuda_graph=False)
+        opt = get_optimizer(opt_name, model, ns)
+        engine.attach_optimizer(opt)
+        tr = Trainer(model, opt, None, engine, 2, torch.device("cuda"))
+        g = torch.Generator().manual_seed(1)
+        losses = []
+        for _ in range(4):
+            step = []
+            for _ in range(2):
+                ids = torch.randint(0, 2048, (2, 128), generator=g).pin_memory()
+                step.append({"input_ids": ids, "labels": ids})
+            losses.append(tr.read_loss(tr.train_step(step)))
+            if offload:
+                big = [v for st in opt.state.values() for v in st.values() if torch.is_tensor(v) and v.numel() > 1]
+                assert big and all(v.device.type == "cpu" and v.is_pinned() for v in big)
+                assert engine._offload.bytes_offloaded > 0
+        params = {n: p.detach().float().clone() for n, p in model.named_parameters()}
+        engine.close()
+        if offload:       # close() brings the state back so it can be saved
+            assert all(v.is_cuda for st in opt.state.values() for v in st.values() if torch.is_tensor(v))
+        return losses, params
+
+    l0, p0 = run(False)
+    l1, p1 = run(True)
+    for a, b in zip(l0, l1):
+        assert abs(a - b) < 2e-2, (l0, l1)
+    for n in p0:
+        c = _cos(p0[n], p1[n]).item()
+        assert c > 0.9999, (n, c)
