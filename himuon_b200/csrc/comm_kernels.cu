@@ -2,9 +2,11 @@
 // stores, per-block flag handshakes with bounded waits, no NCCL and no multicast loads.
 //
 //   peer_barrier     : stream-ordered barrier between the ranks' GPUs (one tiny launch)
-//   allreduce_symm   : one-launch two-shot all-reduce (reduce-scatter by peer loads, all-gather by
-//                      peer stores) with the average / cast fused; replaces the DDP reducer's
-//                      bucketed NCCL all-reduce (reference: train_ddp.py:90, implicit)
+//   allreduce_symm   : one-launch all-reduce with the average / cast fused: two-shot (reduce-scatter by
+//                      peer loads, all-gather by peer stores) for bandwidth-bound regions, one-shot
+//                      (every rank reads everything, no peer stores) for regions up to 256 KiB;
+//                      replaces the DDP reducer's bucketed NCCL all-reduce (reference:
+//                      train_ddp.py:90, implicit)
 //   reduce_replicas  : out = beta * out + scale * sum_r replica_r, the owner-side half of a
 //                      reduce-scatter: for optimizers that need a plain `.grad` (HiMuon fuses this
 //                      step into momentum_tile instead), and for the per-layer-group gradient
@@ -114,12 +116,79 @@ allreduce_symm_kernel(CommPeers peers, CommBufs bufs, long long n_elems, float s
   block_handshake(peers, blockIdx.x, epoch_local, 1, &ok);
 }
 
+// One-shot variant for small, latency-bound regions: every rank reads the whole region from all ranks and keeps the
+// sums in registers, a second handshake tells it that the peers have finished reading its copy, then it writes its
+// own copy.  No peer stores, and no rank waits for data to arrive from another one.
+constexpr int kOneShotVecPerThread = 4;
+template <typename T>
+__global__ void __launch_bounds__(512)
+allreduce_oneshot_kernel(CommPeers peers, CommBufs bufs, long long n_elems, float scale, int* epoch_local) {
+  __shared__ bool ok;
+  constexpr int VEC = 16 / sizeof(T);
+  const int world = peers.world, rank = peers.rank;
+  if (!block_handshake(peers, blockIdx.x, epoch_local, 0, &ok)) return;
+  const long long n_vec = n_elems / VEC;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long v0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  uint4 res[kOneShotVecPerThread];
+#pragma unroll
+  for (int k = 0; k < kOneShotVecPerThread; ++k) {
+    const long long v = v0 + k * stride;
+    if (v >= n_vec) break;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int r = 0; r < world; ++r) {
+      const uint4 x = reinterpret_cast<const uint4*>(bufs.ptr[(rank + r) % world])[v];
+      const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+      if (sizeof(T) == 2) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { acc[2 * q] += bf16_lo(w[q]); acc[2 * q + 1] += bf16_hi(w[q]); }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[q] += __uint_as_float(w[q]);
+      }
+    }
+    if (sizeof(T) == 2) {
+      res[k].x = pack_bf16x2(acc[0] * scale, acc[1] * scale); res[k].y = pack_bf16x2(acc[2] * scale, acc[3] * scale);
+      res[k].z = pack_bf16x2(acc[4] * scale, acc[5] * scale); res[k].w = pack_bf16x2(acc[6] * scale, acc[7] * scale);
+    } else {
+      res[k].x = __float_as_uint(acc[0] * scale); res[k].y = __float_as_uint(acc[1] * scale);
+      res[k].z = __float_as_uint(acc[2] * scale); res[k].w = __float_as_uint(acc[3] * scale);
+    }
+  }
+  if (!block_handshake(peers, blockIdx.x, epoch_local, 1, &ok)) return;   // every rank has read this block's vectors
+#pragma unroll
+  for (int k = 0; k < kOneShotVecPerThread; ++k) {
+    const long long v = v0 + k * stride;
+    if (v >= n_vec) break;
+    reinterpret_cast<uint4*>(bufs.ptr[rank])[v] = res[k];
+  }
+}
+
+// Largest region (bytes) the one-shot kernel takes: 64 blocks x 512 threads x 4 vectors of 16 bytes.
+constexpr long long kOneShotMaxBytes = 64LL * 512 * kOneShotVecPerThread * 16;
+
 void allreduce_symm(const CommPeers& peers, const CommBufs& bufs, long long n_elems, int is_fp32, float scale,
-                    int* epoch_local, int max_blocks, cudaStream_t s) {
+                    int* epoch_local, int max_blocks, cudaStream_t s, int algo) {
   if (n_elems <= 0) return;
   const int vec = is_fp32 ? 4 : 8;
   if (n_elems % (static_cast<long long>(vec) * peers.world))
     throw std::runtime_error("himuon allreduce: element count must be a multiple of (16 bytes * world size)");
+  // algo 0: pick by size (one-shot up to 256 KiB), 1: one-shot, 2: two-shot
+  const long long bytes = n_elems * (is_fp32 ? 4 : 2);
+  if (algo == 1 && bytes > kOneShotMaxBytes)
+    throw std::runtime_error("himuon allreduce: region too large for the one-shot kernel");
+  if (algo == 1 || (algo == 0 && bytes <= (256 << 10))) {
+    const long long n_vec = n_elems / vec;
+    long long blocks = (n_vec + 512LL * kOneShotVecPerThread - 1) / (512LL * kOneShotVecPerThread);
+    if (blocks < 1) blocks = 1;                       // by the size limit above, blocks <= 64 < kCommMaxBlocks
+    if (is_fp32)
+      allreduce_oneshot_kernel<float><<<static_cast<int>(blocks), 512, 0, s>>>(peers, bufs, n_elems, scale, epoch_local);
+    else
+      allreduce_oneshot_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 512, 0, s>>>(peers, bufs, n_elems, scale, epoch_local);
+    return;
+  }
   const long long per_rank_vec = n_elems / vec / peers.world;
   long long blocks = (per_rank_vec + 511) / 512;
   const int cap = max_blocks > 0 ? max_blocks : num_sms();

@@ -74,12 +74,13 @@ class Comm {
   void barrier() { peer_barrier(peers_, epoch_, at::cuda::getCurrentCUDAStream().stream()); }
 
   // In-place all-reduce of the same heap region on every rank.
-  void allreduce(int64_t offset_bytes, int64_t n_elems, bool fp32, double scale, int64_t max_blocks) {
+  void allreduce(int64_t offset_bytes, int64_t n_elems, bool fp32, double scale, int64_t max_blocks, int64_t algo) {
     if (peers_.world == 1) return;
+    TORCH_CHECK(offset_bytes % 16 == 0, "himuon allreduce: the region must start on a 16-byte boundary");
     CommBufs b{};
     for (int r = 0; r < peers_.world; ++r) b.ptr[r] = reinterpret_cast<char*>(heaps_[r]) + offset_bytes;
     allreduce_symm(peers_, b, n_elems, fp32 ? 1 : 0, static_cast<float>(scale), epoch_, static_cast<int>(max_blocks),
-                   at::cuda::getCurrentCUDAStream().stream());
+                   at::cuda::getCurrentCUDAStream().stream(), static_cast<int>(algo));
   }
   // out = beta * out + scale * sum over ranks of the heap region at offset_bytes (out.numel() elements of out's dtype).
   void reduce_to(int64_t offset_bytes, at::Tensor out, double scale, double beta) {
@@ -116,7 +117,8 @@ void bind_symm(py::module_& m) {
       .def("peer_ptr", &Comm::peer_ptr)
       .def_static("flag_bytes", &Comm::flag_bytes)
       .def("barrier", &Comm::barrier)
-      .def("allreduce", &Comm::allreduce)
+      .def("allreduce", &Comm::allreduce, py::arg("offset_bytes"), py::arg("n_elems"), py::arg("fp32"), py::arg("scale"),
+           py::arg("max_blocks") = 0, py::arg("algo") = 0)
       .def("reduce_to", &Comm::reduce_to, py::arg("offset_bytes"), py::arg("out"), py::arg("scale"), py::arg("beta") = 0.0)
       .def("copy_segments", &Comm::copy_segments);
 }

@@ -179,9 +179,9 @@ class CausalLM(nn.Module):
         cos_sin = self._rope(S, input_ids.device)
         h = ops.embedding(input_ids, self.model.embed_tokens.weight).reshape(B * S, -1)
         delta = None
-        # a sharding engine that stages weights or gradients per layer group is told where the layer loop stands
-        engine = getattr(self, "_bank_engine", None)
-        fenced = engine is not None and getattr(engine, "uses_fences", False)
+        # an engine that stages weights or reduces gradients per layer group is told where the layer loop stands
+        engine = getattr(self, "_layer_hooks", None)
+        fenced = engine is not None
         for i, layer in enumerate(self.model.layers):
             if fenced:
                 h, delta = engine.pre_layer(i, h, delta)

@@ -51,31 +51,13 @@ import torch.nn as nn
 
 from .. import ops
 from ..fsdp_bank import Llama3BankScheme, Qwen3BankScheme, unbank_state_dict, wrap_with_banks
+from .fence import LayerFence as _GroupFence
 from .symm import SymmetricHeap, _world
 
 
 class _BankState:
     __slots__ = ("spec", "unit", "n_units", "n_local", "shard", "shard_off", "grad_full", "grad_off", "gathered",
                  "param", "sinks", "pair_sinks", "peer_shards", "ring", "gring", "gring_off", "grad_shard")
-
-
-class _GroupFence(torch.autograd.Function):
-    """Identity on the residual stream ``(h, delta)`` at a layer-group boundary.  Its backward runs exactly when the
-    backward pass crosses the boundary, which is where the engine rotates the staging ring and reduces a finished
-    group's gradients."""
-
-    @staticmethod
-    def forward(ctx, engine, kind, group, h, delta):
-        ctx.engine, ctx.kind, ctx.group = engine, kind, group
-        ctx.set_materialize_grads(False)
-        if delta is None:
-            return h.view_as(h), None
-        return h.view_as(h), delta.view_as(delta)
-
-    @staticmethod
-    def backward(ctx, gh, gd):
-        ctx.engine._on_backward_boundary(ctx.kind, ctx.group)
-        return None, None, None, gh, gd
 
 
 class ShardedEngine:
@@ -207,6 +189,7 @@ class ShardedEngine:
         if self.cuda:
             torch.cuda.empty_cache()
         object.__setattr__(model, "_bank_engine", self if self.banks is not None else None)
+        object.__setattr__(model, "_layer_hooks", self if self.uses_fences else None)
         self.materialize_grads = False    # True: produce .grad for bank shards (optimizers without the fused path)
         self._copy_table = None
         self._offload = None

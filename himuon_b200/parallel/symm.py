@@ -101,15 +101,18 @@ class SymmetricHeap:
         else:
             dist.barrier()
 
-    def allreduce_(self, tensor: torch.Tensor, offset: int, scale: float, max_blocks: int = 0):
-        """In-place sum over ranks of the region ``tensor`` (at ``offset``) times ``scale``."""
+    def allreduce_(self, tensor: torch.Tensor, offset: int, scale: float, max_blocks: int = 0, algo: int = 0):
+        """In-place sum over ranks of the region ``tensor`` (at ``offset``) times ``scale``.  ``algo``: 0 picks the
+        one-shot kernel up to 256 KiB and the two-shot kernel above, 1 / 2 force one of them; ``max_blocks`` caps the
+        two-shot grid (a small grid leaves the SMs to a compute stream that runs beside it)."""
         if self.world == 1:
             if scale != 1.0:
                 tensor.mul_(scale)
             return
         if self.cuda:
             from ..ops import _count
-            self.comm.allreduce(offset, tensor.numel(), tensor.dtype == torch.float32, float(scale), int(max_blocks))
+            self.comm.allreduce(offset, tensor.numel(), tensor.dtype == torch.float32, float(scale), int(max_blocks),
+                                int(algo))
             _count()
         else:
             work = tensor.float() if tensor.dtype == torch.bfloat16 else tensor

@@ -186,7 +186,7 @@ class Trainer:
         self.graph_microbatch = bool(graph_microbatch) and self.device.type == "cuda"
         self.graph_warmup_steps = int(graph_warmup_steps)
         self._steps_done = 0
-        self._mb_graphs = {}          # first(bool) -> (graph, static loss, launches, sinks written)
+        self._mb_graphs = {}          # (first, own graph for the sync step) -> (graph, static loss, launches, sinks written, engine state)
         self._mb_static = None
         self._mb_pool = None
         if self.graph_microbatch:
@@ -213,14 +213,18 @@ class Trainer:
             self._mb_static = {"input_ids": torch.empty_like(ids), "labels": torch.empty_like(labels)}
         self._mb_static["input_ids"].copy_(ids)
         self._mb_static["labels"].copy_(labels)
-        entry = self._mb_graphs.get(first)
+        # an engine whose synchronising micro-step differs from the accumulating ones (it starts collectives from
+        # inside backward) gets a graph of its own for it
+        key = (first, bool(sync and getattr(self.engine, "graph_key_sync", False)))
+        entry = self._mb_graphs.get(key)
         if entry is None:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             n0 = ops.launch_count()
             ops.GradSink.start_log()
+            ctx = self.engine.no_sync() if (self.engine is not None and not sync) else nullcontext()
             try:
-                with torch.cuda.graph(graph, pool=self._mb_pool):
+                with ctx, torch.cuda.graph(graph, pool=self._mb_pool):
                     loss = self.model(self._mb_static["input_ids"], labels=self._mb_static["labels"]).loss
                     (loss / self.grad_acc).backward()
                     static_loss = loss.detach()
@@ -228,8 +232,10 @@ class Trainer:
                 written = ops.GradSink.stop_log()
             self._mb_pool = graph.pool()
             # the capture ran the wrappers once (launches counted); it also tells which gradient sinks a replay writes
-            entry = (graph, static_loss, ops.launch_count() - n0, written)
-            self._mb_graphs[first] = entry
+            # and what host-side state the engine's hooks left behind
+            state = self.engine.graph_capture_state() if hasattr(self.engine, "graph_capture_state") else None
+            entry = (graph, static_loss, ops.launch_count() - n0, written, state)
+            self._mb_graphs[key] = entry
         else:
             ops.add_launches(entry[2])
         entry[0].replay()
@@ -237,6 +243,8 @@ class Trainer:
             sink = ref_sink()
             if sink is not None:
                 sink.fresh = False
+        if entry[4] is not None:
+            self.engine.graph_replay_state(entry[4])
         return entry[1].clone()
 
     def _to_device(self, batch):

@@ -94,7 +94,9 @@ def scenario_train(mode, optimizer_name, device):
         mode = "fsdp"
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
-        engine = DataParallelEngine(model, timeout_s=30.0)
+        # 5 layers in buckets of 2: three buckets, the last one short
+        engine = DataParallelEngine(model, timeout_s=30.0, bucket_layers=2, overlap="serial" not in opts)
+        assert engine.overlap == (world > 1 and "serial" not in opts)
     lr = 1e-3 if optimizer_name == "adamw" else 0.02
     ns = argparse.Namespace(lr=lr, weight_decay=0.1, tile_size=128, cuda_graph=True, cuda_graph_warmup=1)
     opt = get_optimizer(optimizer_name, model, ns)
@@ -110,8 +112,10 @@ def scenario_train(mode, optimizer_name, device):
     all_losses = [None] * world
     dist.all_gather_object(all_losses, losses)
     sd = engine.full_state_dict() if mode == "fsdp" else {k: v.detach().cpu() for k, v in model.state_dict().items()}
+    if mode == "ddp" and engine.overlap:
+        assert engine.overlapped_launches >= engine.n_buckets, engine.overlapped_launches
     if "graph" in opts:
-        assert set(trainer._mb_graphs) == {True, False}, "the micro-batch graphs were not captured"
+        assert {k[0] for k in trainer._mb_graphs} == {True, False}, "the micro-batch graphs were not captured"
     if rank == 0:
         torch.manual_seed(0)
         ref_model = CausalLM(_cfg(layers)).to(device, torch.bfloat16)

@@ -34,7 +34,8 @@ def test_peer_memory_collectives():
                                       ("fsdp-peer", "himuon"), ("fsdp:ring:replicated", "himuon"),
                                       ("fsdp:ring:replicated:graph", "himuon"), ("fsdp:gathered:sharded", "himuon"),
                                       ("fsdp:ring:sharded:graph:ckpt", "himuon"), ("fsdp:ring:sharded", "adamw"),
-                                      ("fsdp:ring:sharded", "muon-fsdp")])
+                                      ("fsdp:ring:sharded", "muon-fsdp"), ("ddp:overlap:graph", "himuon"),
+                                      ("ddp:serial", "adamw")])
 def test_multi_gpu_training_matches_single_process(mode, opt):
     r = _run(2, "train", mode, opt)
     assert "PARITY OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
