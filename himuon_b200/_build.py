@@ -21,6 +21,7 @@ CUDA_SOURCES = [
     "attention_kv64_sm100.cu", "attention_bwd_sm100.cu",
     "ns5_sm100.cu",
     "comm_kernels.cu",
+    "soap_kernels.cu",
     "rmsnorm_bwd_noalloc.cu",
 ]
 CPP_SOURCES = ["bindings.cpp", "symm.cpp"]

@@ -252,7 +252,30 @@ static void ns5_fused(const at::Tensor& x, at::Tensor& out, int64_t steps, doubl
 
 static int64_t status(bool reset) { return himuon::read_status_word(reset); }
 
+static void soap_moments(const at::Tensor& g, const at::Tensor& g_rot, at::Tensor& m, at::Tensor& v, double b1, double b2) {
+  HM_CHECK(g.is_cuda() && is_bf16(g) && is_bf16(g_rot) && is_bf16(m) && is_bf16(v), "soap_moments: bf16 CUDA tensors");
+  HM_CHECK(g.is_contiguous() && g_rot.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "soap_moments: contiguous tensors");
+  HM_CHECK(g.numel() == g_rot.numel() && g.numel() == m.numel() && g.numel() == v.numel() && g.numel() % 8 == 0,
+           "soap_moments: equal element counts, multiples of 8");
+  for (const at::Tensor* t : {&g, &g_rot, &m, &v})
+    HM_CHECK(reinterpret_cast<uintptr_t>(t->data_ptr()) % 16 == 0, "soap_moments: 16-byte aligned tensors");
+  const c10::cuda::CUDAGuard guard(g.device());
+  himuon::soap_moments(g.data_ptr(), g_rot.data_ptr(), m.data_ptr(), v.data_ptr(), g.numel(), (float)b1, (float)b2, cur_stream());
+}
+static void soap_ratio(const at::Tensor& m_rot, const at::Tensor& v, at::Tensor& out, double eps) {
+  HM_CHECK(m_rot.is_cuda() && is_bf16(m_rot) && is_bf16(v) && is_bf16(out), "soap_ratio: bf16 CUDA tensors");
+  HM_CHECK(m_rot.is_contiguous() && v.is_contiguous() && out.is_contiguous(), "soap_ratio: contiguous tensors");
+  HM_CHECK(m_rot.numel() == v.numel() && m_rot.numel() == out.numel() && m_rot.numel() % 8 == 0,
+           "soap_ratio: equal element counts, multiples of 8");
+  for (const at::Tensor* t : {&m_rot, &v, &out})
+    HM_CHECK(reinterpret_cast<uintptr_t>(t->data_ptr()) % 16 == 0, "soap_ratio: 16-byte aligned tensors");
+  const c10::cuda::CUDAGuard guard(m_rot.device());
+  himuon::soap_ratio(m_rot.data_ptr(), v.data_ptr(), out.data_ptr(), m_rot.numel(), (float)eps, cur_stream());
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("soap_moments", &soap_moments);
+  m.def("soap_ratio", &soap_ratio);
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("aux") = py::none(), py::arg("trans_a") = false,
         py::arg("trans_b") = false, py::arg("alpha") = 1.0, py::arg("beta") = 0.0, py::arg("round_acc") = false,
         py::arg("max_ctas") = 0, py::arg("symmetric") = false);

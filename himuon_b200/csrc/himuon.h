@@ -99,6 +99,12 @@ void adamw_multi(const AdamEntry* entries, int n_entries, long long total_units,
                  int mode, int param_fp32, int state_fp32, cudaStream_t stream);
 void adamw_step_advance(float* step, cudaStream_t stream);
 
+// SOAP in the eigenbasis (bf16, contiguous, 16-byte aligned, element counts multiples of 8):
+// m <- b1*m + (1-b1)*g ; v <- b2*v + (1-b2)*g_rot^2            and            out <- m_rot / (sqrt(v) + eps)
+void soap_moments(const void* g, const void* g_rot, void* m, void* v, long long n_elems, float b1, float b2,
+                  cudaStream_t s);
+void soap_ratio(const void* m_rot, const void* v, void* out, long long n_elems, float eps, cudaStream_t s);
+
 // ---------------------------------------------------------------- model kernels
 // With `delta`/`h_out`: h_out = bf16(x + delta) is written and normalised instead of x (fused residual update).
 void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s,

@@ -6,8 +6,13 @@ Constructor, defaults and state keys (``step``, ``exp_avg``, ``exp_avg_sq``, ``G
 ``precondition_frequency`` steps (with the second moment re-ordered to follow the sorted basis),
 and a first step that only gathers statistics.  Single-process / DDP only, as upstream.
 
-The eigendecompositions go through ``torch.linalg`` (cuSOLVER on CUDA): SOAP is not part of the
-sm_100a kernel set.
+On a CUDA device, 2-D bf16 parameters whose sides are multiples of 8 take the kernel path
+(``_step_matrix_cuda``): the six rotations of a step (``Q_L^T G Q_R`` for the gradient and for the first moment,
+``Q_L R Q_R^T`` back) and the two Gram-matrix updates are tcgen05 GEMMs - the Gram EMA (``GG <- beta GG +
+(1-beta) G G^T``, fp32) and the parameter update with its weight decay are fused into GEMM epilogues - and the
+moment updates and the Adam ratio in the eigenbasis are the ``soap_moments`` / ``soap_ratio`` kernels.  The
+eigendecompositions (``eigh`` once, power iteration + ``qr`` every ``precondition_frequency`` steps) stay on
+``torch.linalg`` (cuSOLVER), as does every other parameter shape.
 """
 
 from __future__ import annotations
@@ -111,6 +116,8 @@ class SOAP(Optimizer):
             if group["precondition_1d"] and grad.shape[0] <= group["max_precond_dim"]:
                 g = grad.float()
                 state["GG"][0].lerp_(torch.outer(g, g), 1 - beta)
+        elif self._kernel_ok(grad, grad, state, group):
+            self._gram_update_cuda(grad, state)
         else:
             work, _ = self._work_view(grad, group)
             work = work.float()
@@ -177,6 +184,52 @@ class SOAP(Optimizer):
     def project_back(self, grad, state, group):
         return self._rotate(grad, state, group, back=True)
 
+    # ------------------------------------------------------------------ kernel path (2-D bf16 matrices on CUDA)
+    @staticmethod
+    def _kernel_ok(p, grad, state, group) -> bool:
+        if not (grad.is_cuda and grad.dtype == torch.bfloat16 and p.dtype == torch.bfloat16 and grad.dim() == 2):
+            return False
+        if group["merge_dims"] or group["normalize_grads"] or not grad.is_contiguous() or not p.is_contiguous():
+            return False
+        m, n = grad.shape
+        if m % 8 or n % 8 or max(m, n) > group["max_precond_dim"]:
+            return False
+        gg = state.get("GG")
+        return gg is None or all(len(g) for g in gg)
+
+    @staticmethod
+    def _q16(state):
+        """bf16 copies of the eigenbases for the rotation GEMMs (rebuilt whenever the bases change)."""
+        if state.get("_Q16_src") is not state["Q"]:
+            state["_Q16"] = [q.to(torch.bfloat16).contiguous() for q in state["Q"]]
+            state["_Q16_src"] = state["Q"]
+        return state["_Q16"]
+
+    def _gram_update_cuda(self, grad, state):
+        from .. import ops
+        beta = state["shampoo_beta"]
+        ggl, ggr = state["GG"]
+        ops.gemm(grad, grad, trans_b=True, alpha=1 - beta, beta=beta, aux=ggl, out=ggl)      # GG_L <- b GG_L + (1-b) G G^T
+        ops.gemm(grad, grad, trans_a=True, alpha=1 - beta, beta=beta, aux=ggr, out=ggr)      # GG_R <- b GG_R + (1-b) G^T G
+
+    def _step_matrix_cuda(self, p, grad, state, group):
+        from .. import _ext, ops
+        e = _ext.ext()
+        b1, b2 = group["betas"]
+        ql, qr = self._q16(state)
+        g_rot = ops.gemm(ops.gemm(ql, grad, trans_a=True), qr)                 # Q_L^T G Q_R
+        state["step"] += 1
+        e.soap_moments(grad, g_rot, state["exp_avg"], state["exp_avg_sq"], b1, b2)
+        m_rot = ops.gemm(ops.gemm(ql, state["exp_avg"], trans_a=True), qr)     # Q_L^T M Q_R
+        e.soap_ratio(m_rot, state["exp_avg_sq"], m_rot, group["eps"])
+        ops._count(2)
+        step_size = group["lr"]
+        if group["correct_bias"]:
+            step_size = step_size * (1 - b2 ** state["step"]) ** 0.5 / (1 - b1 ** state["step"])
+        keep = 1.0 - group["lr"] * group["weight_decay"] if group["weight_decay"] > 0.0 else 1.0
+        # p <- (p - step * Q_L R Q_R^T) * (1 - lr*wd), the update and the decoupled decay in the last GEMM's epilogue
+        ops.gemm(ops.gemm(ql, m_rot), qr, trans_b=True, alpha=-step_size * keep, beta=keep, aux=p.data, out=p.data)
+
     # ------------------------------------------------------------------ step
     @torch.no_grad()
     def step(self, closure=None):
@@ -196,6 +249,10 @@ class SOAP(Optimizer):
                 if "Q" not in state:
                     # first step: gather statistics only, never project with the current gradient
                     self.init_preconditioner(grad, state, group)
+                    self.update_preconditioner(grad, state, group)
+                    continue
+                if self._kernel_ok(p, grad, state, group):
+                    self._step_matrix_cuda(p, grad, state, group)
                     self.update_preconditioner(grad, state, group)
                     continue
                 g_rot = self.project(grad, state, group)

@@ -31,7 +31,7 @@ from torch.utils.data import DataLoader
 from .dataset import SyntheticTokenDataset, ToyDataset
 from .model import count_model_parameters, count_num_training_tokens, get_model_and_tokenizer
 from .optim import get_optimizer
-from .utils import TimeBudget, merge_kv_args, seed_everything
+from .utils import PhaseTimer, TimeBudget, merge_kv_args, seed_everything
 
 
 # ------------------------------------------------------------------------------------------- CLI
@@ -169,7 +169,8 @@ class Trainer:
     """
 
     def __init__(self, model, optimizer, scheduler=None, engine=None, grad_acc: int = 1, device=None,
-                 autocast_dtype=None, graph_microbatch: bool = False, graph_warmup_steps: int = 2):
+                 autocast_dtype=None, graph_microbatch: bool = False, graph_warmup_steps: int = 2,
+                 phase_timing: bool = False):
         self.model, self.optimizer, self.scheduler, self.engine = model, optimizer, scheduler, engine
         self.grad_acc = int(grad_acc)
         self.device = device if device is not None else next(model.parameters()).device
@@ -179,6 +180,8 @@ class Trainer:
             model.set_loss_scale(1.0 / self.grad_acc)
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        # per-phase device time (CUDA events) of every step when enabled; the phases are NVTX ranges either way
+        self.phases = PhaseTimer(phase_timing, self.device if self.device.type == "cuda" else None)
         # Optional: forward+backward of one micro-batch replayed from a CUDA graph (removes ~30k kernel launches'
         # worth of host work per step).  Two graphs are captured after `graph_warmup_steps` eager steps: one for
         # the first micro-batch of a step (weight gradients overwrite) and one for the others (they accumulate).
@@ -258,23 +261,29 @@ class Trainer:
     def train_step(self, host_batches) -> torch.Tensor:
         assert len(host_batches) == self.grad_acc
         total = None
+        ph = self.phases
         for i, hb in enumerate(host_batches):
-            batch = self._to_device(hb)
+            with ph.phase("h2d"):
+                batch = self._to_device(hb)
             sync = i == self.grad_acc - 1
-            if self.graph_microbatch:
-                loss = self._graph_microbatch(batch, first=(i == 0), sync=sync)
-            else:
-                loss = self._eager_microbatch(batch, sync)
+            with ph.phase("forward_backward"):
+                if self.graph_microbatch:
+                    loss = self._graph_microbatch(batch, first=(i == 0), sync=sync)
+                else:
+                    loss = self._eager_microbatch(batch, sync)
             total = loss if total is None else total + loss
         if self.engine is not None:
-            self.engine.finish_backward()
-        self.optimizer.step()
+            with ph.phase("grad_reduce"):
+                self.engine.finish_backward()
+        with ph.phase("optimizer"):
+            self.optimizer.step()
         if self.scheduler is not None:
             self.scheduler.step()
-        if self.engine is not None:
-            self.engine.zero_grad(set_to_none=self.zero_set_to_none)
-        else:
-            self.optimizer.zero_grad(set_to_none=self.zero_set_to_none)
+        with ph.phase("regather_reset"):
+            if self.engine is not None:
+                self.engine.zero_grad(set_to_none=self.zero_set_to_none)
+            else:
+                self.optimizer.zero_grad(set_to_none=self.zero_set_to_none)
         self._steps_done += 1
         return total / self.grad_acc
 
@@ -410,7 +419,8 @@ def run_training(args, mode: str) -> dict:
     apply_reconfigure(0)
 
     trainer = Trainer(model, optimizer, scheduler, engine, args.gradient_accumulation_steps, device,
-                      graph_microbatch=bool(getattr(args, "cuda_graph_step", False)))
+                      graph_microbatch=bool(getattr(args, "cuda_graph_step", False)),
+                      phase_timing=bool(getattr(args, "time_stats", False)))
     trainer.zero_set_to_none = not args.cuda_graph if hasattr(optimizer, "reconfigure") else True
     if trainer.graph_microbatch:
         trainer.zero_set_to_none = False       # captured graphs write into the gradient tensors that exist at capture
@@ -441,6 +451,9 @@ def run_training(args, mode: str) -> dict:
             metrics["step_time"] = now - t_step
             metrics["tokens_per_sec"] = tokens_per_step / max(1e-9, now - t_step)
             t_step = now
+            for name, ms in trainer.phases.summary().items():       # device time per phase, max over ranks
+                metrics[f"ms_{name}"] = round(ms, 3)
+            trainer.phases.reset()
         if args.eval_interval and global_step % args.eval_interval == 0:
             metrics["eval_loss"] = trainer.evaluate(eval_batches)
         if logger is not None:

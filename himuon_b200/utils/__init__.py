@@ -6,7 +6,7 @@ plus device-side timing helpers used by the benchmarks.
 """
 
 from .misc import TimeBudget, merge_kv_args, parse_kv_args, seed_everything
-from .timing import ClockSampler, cuda_time_ms, l2_flush_buffer, max_over_ranks
+from .timing import ClockSampler, PhaseTimer, cuda_time_ms, l2_flush_buffer, max_over_ranks, nvtx_range
 
 __all__ = [
     "seed_everything",
@@ -17,4 +17,6 @@ __all__ = [
     "max_over_ranks",
     "l2_flush_buffer",
     "ClockSampler",
+    "PhaseTimer",
+    "nvtx_range",
 ]

@@ -51,6 +51,74 @@ def max_over_ranks(value: float, device=None) -> float:
     return float(t.item())
 
 
+class nvtx_range:
+    """``with nvtx_range("optimizer"):`` - an NVTX range around a phase of the step, visible on the timeline of any
+    NVTX-aware profiler.  Does nothing without CUDA."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self._on = torch.cuda.is_available()
+
+    def __enter__(self):
+        if self._on:
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if self._on:
+            torch.cuda.nvtx.range_pop()
+
+
+class PhaseTimer:
+    """Per-phase device time of a training step (host-to-device copies, forward+backward, gradient reduction,
+    optimizer, re-gather + reset), from CUDA events on the launching stream; every phase is also an NVTX range.
+
+    ``with timer.phase("optimizer"): ...`` brackets a phase; ``timer.summary()`` synchronises once and returns the
+    milliseconds per phase accumulated since the last ``reset()`` (each the maximum over ranks when a process group
+    is up).  Disabled timers cost nothing: no events, no synchronisation.
+    """
+
+    def __init__(self, enabled: bool = False, device=None):
+        self.enabled = bool(enabled) and torch.cuda.is_available()
+        self.device = device
+        self._events: dict[str, list] = {}
+
+    class _Phase:
+        def __init__(self, timer, name):
+            self.timer, self.name = timer, name
+            self.range = nvtx_range(name)
+
+        def __enter__(self):
+            self.range.__enter__()
+            if self.timer.enabled:
+                self.start = torch.cuda.Event(enable_timing=True)
+                self.start.record()
+            return self
+
+        def __exit__(self, *exc):
+            if self.timer.enabled:
+                end = torch.cuda.Event(enable_timing=True)
+                end.record()
+                self.timer._events.setdefault(self.name, []).append((self.start, end))
+            self.range.__exit__(*exc)
+
+    def phase(self, name: str):
+        return PhaseTimer._Phase(self, name)
+
+    def reset(self):
+        self._events = {}
+
+    def summary(self, reduce_over_ranks: bool = True) -> dict:
+        if not self.enabled or not self._events:
+            return {}
+        torch.cuda.synchronize(self.device)
+        out = {}
+        for name, pairs in self._events.items():
+            ms = sum(a.elapsed_time(b) for a, b in pairs)
+            out[name] = max_over_ranks(ms) if reduce_over_ranks else ms
+        return out
+
+
 class ClockSampler:
     """Samples ``nvidia-smi`` SM clocks and throttle reasons on a background thread.
 

@@ -197,3 +197,56 @@ def test_resume_from_state_dict_continues_bias_correction(which):
     torch.cuda.synchronize()
     for a, b in zip(list(m1.parameters()) + [b1], list(m2.parameters()) + [b2]):
         assert torch.allclose(a.float(), b.float(), atol=2e-3, rtol=1e-2), (a.float() - b.float()).abs().max()
+
+
+def _cosine(a, b):
+    a, b = a.float().flatten().cpu(), b.float().flatten().cpu()
+    return float(torch.dot(a, b) / (a.norm() * b.norm() + 1e-12))
+
+
+@pytest.mark.parametrize("which", ["soap", "muon", "himuon-legacy"])
+def test_baseline_optimizers_step_on_the_kernels_like_their_cpu_paths(which):
+    """SOAP (rotations, Gram statistics and update on the GEMM, moments in the soap_* kernels), Muon and HiMuonLegacy
+    (Newton-Schulz on tcgen05) take several steps on bf16 CUDA parameters; the updates must follow the same optimizer
+    stepping fp32 copies of the same parameters and gradients on the CPU."""
+    from himuon_b200 import ops
+    from himuon_b200.optimizers import SOAP, HiMuonLegacy, Muon
+
+    shapes = [(256, 384), (128, 128), (320, 136)]
+
+    def build(device, dtype):
+        torch.manual_seed(0)
+        model = make_linear_model(shapes, dtype=torch.float32)
+        with torch.no_grad():
+            for p in model.parameters():
+                p.copy_(p.bfloat16().float())
+        model = model.to(device=device, dtype=dtype)
+        if which == "soap":
+            opt = SOAP(model.parameters(), lr=3e-3, precondition_frequency=3, weight_decay=0.01)
+        elif which == "muon":
+            opt = Muon([{"params": list(model.parameters())}], lr=0.02, weight_decay=0.1)
+        else:
+            opt = HiMuonLegacy([{"params": list(model.parameters())}], lr=0.02, weight_decay=0.1, tile_size=128)
+        return model, opt
+
+    gpu_model, gpu_opt = build("cuda", torch.bfloat16)
+    cpu_model, cpu_opt = build("cpu", torch.float32)
+    start = [p.detach().float().cpu().clone() for p in gpu_model.parameters()]
+    before = ops.launch_count()
+    for s in range(6):
+        g = torch.Generator().manual_seed(100 + s)
+        for pg, pc in zip(gpu_model.parameters(), cpu_model.parameters()):
+            val = torch.randn(pc.shape, generator=g).bfloat16()
+            pg.grad = val.cuda()
+            pc.grad = val.float()
+        gpu_opt.step()
+        cpu_opt.step()
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert ops.launch_count() - before > 6 * len(shapes), "the kernel path did not run"
+    for p0, pg, pc in zip(start, gpu_model.parameters(), cpu_model.parameters()):
+        dg, dc = pg.detach().float().cpu() - p0, pc.detach() - p0
+        assert torch.isfinite(dg).all()
+        c = _cosine(dg, dc)
+        assert c > 0.97, (which, tuple(pc.shape), c)
+        assert abs(float(dg.norm() / dc.norm()) - 1.0) < 0.1, (which, float(dg.norm()), float(dc.norm()))
