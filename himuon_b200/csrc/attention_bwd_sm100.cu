@@ -14,7 +14,6 @@
 // Requires S to be a multiple of 128; the per-row statistics (log-sum-exp, delta) arrive by bulk copies.
 #include "attention_common.cuh"
 
-#include <cstdlib>
 #include <string>
 
 namespace himuon {
@@ -417,23 +416,13 @@ flash_bwd_dq_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   }
 }
 
-// HIMUON_ATTN_DKV=legacy keeps the kernels of attention_sm100.cu / attention_kv64_sm100.cu for every shape;
-// HIMUON_ATTN_DQ=legacy does so for the dQ pass only.
+// The pipelined kernels take sequence lengths that are multiples of 128 with 16-byte aligned row statistics; other
+// shapes run the kernels of attention_sm100.cu / attention_kv64_sm100.cu.
 bool flash_bwd_dkv_t_supported(const AttnArgs& a) {
-  static const bool enabled = [] {
-    const char* e = getenv("HIMUON_ATTN_DKV");
-    return !(e && std::string(e) == "legacy");
-  }();
-  return enabled && a.S % AT == 0 && (reinterpret_cast<uintptr_t>(a.lse) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.delta) & 15) == 0;
+  return a.S % AT == 0 && (reinterpret_cast<uintptr_t>(a.lse) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.delta) & 15) == 0;
 }
 
-bool flash_bwd_dq_t_supported(const AttnArgs& a) {
-  static const bool enabled = [] {
-    const char* e = getenv("HIMUON_ATTN_DQ");
-    return !(e && std::string(e) == "legacy");
-  }();
-  return enabled && flash_bwd_dkv_t_supported(a);
-}
+bool flash_bwd_dq_t_supported(const AttnArgs& a) { return flash_bwd_dkv_t_supported(a); }
 
 // `p` carries the output pointers and the split_heads flag chosen by the caller; the grid's y extent is the number of
 // query heads (split_heads) or KV heads.

@@ -1,11 +1,10 @@
 // Flash attention forward and dQ kernels with 64-wide KV blocks.
 //
-// Same algorithm and tile layouts as attention_sm100.cu, but K/V arrive in blocks of 64 positions: shared memory drops
-// to 96 KB and the TMEM footprint to 256 columns, so two CTAs run on every SM and one CTA's tensor-core work overlaps
-// the other's softmax (the 128-wide kernels run one CTA per SM and are latency bound on the softmax threads).
+// K/V arrive in blocks of 64 positions: shared memory stays at 96 KB and the TMEM footprint at 256 columns, so two
+// CTAs run on every SM and one CTA's tensor-core work overlaps the other's softmax.  The dQ kernel here serves
+// sequence lengths that are not a multiple of 128; the others take the pipelined kernel of attention_bwd_sm100.cu.
 #include "attention_common.cuh"
 
-#include <cstdlib>
 #include <string>
 
 namespace himuon {
@@ -28,222 +27,13 @@ __device__ __forceinline__ uint32_t p_off(int r, int c16) {                  // 
   return static_cast<uint32_t>(r * 128 + ((c16 ^ (r & 7)) << 4));
 }
 
-struct Fwd64Bars {
-  uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full[2], s_empty[2], p_ready, o_done;
-  uint32_t tmem_slot;
-  int abort_flag;
-};
-
-// ================================================================================================ forward
-__global__ void __launch_bounds__(192, 2)
-flash_fwd64_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, AttnDev p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = align_up_1024(smem_raw);
-  uint8_t* sQ = smem;                          // 32 KB
-  uint8_t* sK = smem + TILE_BYTES;             // 2 stages x 16 KB
-  uint8_t* sV = sK + 2 * KV_TILE;              // 1 stage  x 16 KB
-  uint8_t* sP = sV + KV_TILE;                  // 16 KB
-  Fwd64Bars* bars = reinterpret_cast<Fwd64Bars*>(sP + P_BYTES);
-  volatile int* abort_flag = &bars->abort_flag;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int sblk, h, b;
-  attn_block_coords(sblk, h, b);
-  const int qb = gridDim.x - 1 - sblk;         // heavy (late) query blocks first
-  const int hk = h / (p.Hq / p.Hkv);
-  int nkv = (qb + 1) * (AT / BKV);             // KV blocks up to and including the diagonal
-  const int nkv_all = (p.S + BKV - 1) / BKV;
-  if (nkv > nkv_all) nkv = nkv_all;
-
-  if (threadIdx.x == 0) {
-    mbar_init(&bars->q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1);
-      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_empty[i], 128);
-    }
-    mbar_init(&bars->v_full, 1); mbar_init(&bars->v_empty, 1);
-    mbar_init(&bars->p_ready, 128);
-    mbar_init(&bars->o_done, 1);
-    bars->abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 1) tmem_alloc(&bars->tmem_slot, 256);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = bars->tmem_slot;
-  const uint32_t tS0 = tmem, tO = tmem + 128;   // S buffers at columns 0 and 64, O at 128
-
-  if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(&bars->q_full, TILE_BYTES);
-      tma_load_4d(sQ, &tmQ, &bars->q_full, 0, h, qb * AT, b);
-      tma_load_4d(sQ + HALF_BYTES, &tmQ, &bars->q_full, 64, h, qb * AT, b);
-      for (int j = 0; j < nkv; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&bars->k_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, p.status, 4)) break;
-        mbar_expect_tx(&bars->k_full[st], KV_TILE);
-        tma_load_4d(sK + st * KV_TILE, &tmK, &bars->k_full[st], 0, hk, j * BKV, b);
-        tma_load_4d(sK + st * KV_TILE + KV_HALF, &tmK, &bars->k_full[st], 64, hk, j * BKV, b);
-        if (!mbar_wait(&bars->v_empty, (j & 1) ^ 1, abort_flag, p.status, 4)) break;
-        mbar_expect_tx(&bars->v_full, KV_TILE);
-        tma_load_4d(sV, &tmV, &bars->v_full, 0, hk, j * BKV, b);
-        tma_load_4d(sV + KV_HALF, &tmV, &bars->v_full, 64, hk, j * BKV, b);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, BKV, false, false);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, false, true);
-      const uint32_t q_base = smem_u32(sQ), p_base = smem_u32(sP), v_base = smem_u32(sV);
-      bool ok = mbar_wait(&bars->q_full, 0, abort_flag, p.status, 4);
-      auto issue_s = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!mbar_wait(&bars->k_full[st], (j >> 1) & 1, abort_flag, p.status, 4)) return false;
-        if (j >= 2 && !mbar_wait(&bars->s_empty[st], ((j >> 1) - 1) & 1, abort_flag, p.status, 4)) return false;
-        tc_fence_after();
-        const uint32_t k_base = smem_u32(sK + st * KV_TILE);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ss(tS0 + st * BKV, desc_kmajor(q_base, ks), kv_desc_kmajor(k_base, ks), idesc_s, ks > 0 ? 1u : 0u);
-        umma_commit(&bars->k_empty[st]);
-        umma_commit(&bars->s_full[st]);
-        return true;
-      };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; ok && j < nkv; ++j) {
-        if (j + 1 < nkv) { ok = issue_s(j + 1); if (!ok) break; }
-        if (!mbar_wait(&bars->p_ready, j & 1, abort_flag, p.status, 4)) break;
-        if (!mbar_wait(&bars->v_full, j & 1, abort_flag, p.status, 4)) break;
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < BKV / 16; ++ks)
-          umma_ss(tO, p_desc_kmajor(p_base, ks), kv_desc_mnmajor(v_base, ks), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&bars->v_empty);
-        umma_commit(&bars->o_done);
-      }
-    }
-  } else {
-    // ------------------------------------------------------------ softmax / epilogue: one thread per query row
-    const int row = (warp & 3) * 32 + lane;
-    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const int q_idx = qb * AT + row;
-    float m_used = -INFINITY, l = 0.f;
-    bool ok = true;
-    for (int j = 0; j < nkv; ++j) {
-      const int st = j & 1;
-      if (!mbar_wait(&bars->s_full[st], (j >> 1) & 1, abort_flag, p.status, 4)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t tS = tS0 + st * BKV + lane_off;
-      const int kv0 = j * BKV;
-      const bool diag = (kv0 + BKV - 1 > qb * AT);       // the block reaches past the first row of this query tile
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          float s = __uint_as_float(v[t]) * p.scale_log2;
-          if (diag && (kv0 + c * 32 + t > q_idx)) s = -INFINITY;
-          mx = fmaxf(mx, s);
-        }
-      }
-      const float m_new = fmaxf(m_used, mx);
-      const bool need = (j > 0) && (m_new - m_used > 8.f);
-      const bool warp_need = __any_sync(0xffffffffu, need);
-      float alpha = 1.f;
-      if (j == 0) {
-        m_used = m_new;
-      } else if (warp_need) {
-        alpha = exp2f(m_used - m_new);
-        m_used = m_new;
-      }
-      if (j > 0) {
-        if (!mbar_wait(&bars->o_done, (j - 1) & 1, abort_flag, p.status, 4)) { ok = false; break; }
-        tc_fence_after();
-        if (warp_need) {
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t v[32];
-            tmem_ld32(tO + lane_off + c * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
-            tmem_st32(tO + lane_off + c * 32, v);
-          }
-          tmem_st_wait();
-          l *= alpha;
-        }
-      }
-      float rs = 0.f;
-#pragma unroll
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + c * 32, v);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int t = 0; t < 32; t += 2) {
-          float p0 = exp2f(__uint_as_float(v[t]) * p.scale_log2 - m_used);
-          float p1 = exp2f(__uint_as_float(v[t + 1]) * p.scale_log2 - m_used);
-          if (diag) {
-            if (kv0 + c * 32 + t > q_idx) p0 = 0.f;
-            if (kv0 + c * 32 + t + 1 > q_idx) p1 = 0.f;
-          }
-          pk[t >> 1] = pack_bf16x2(p0, p1);
-          rs += bf16_lo(pk[t >> 1]) + bf16_hi(pk[t >> 1]);
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          *reinterpret_cast<uint4*>(sP + p_off(row, c * 4 + q)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-      }
-      l += rs;
-      tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive(&bars->s_empty[st]);
-      mbar_arrive(&bars->p_ready);
-    }
-    if (ok && mbar_wait(&bars->o_done, (nkv - 1) & 1, abort_flag, p.status, 4)) {
-      tc_fence_after();
-      const float inv = 1.f / l;
-      const bool row_ok = q_idx < p.S;
-      __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.o) + (static_cast<long long>(b) * p.S + q_idx) * p.ld_o + h * HD;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tO + lane_off + c * 32, v);
-        tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 o4;
-            o4.x = pack_bf16x2(__uint_as_float(v[8 * q + 0]) * inv, __uint_as_float(v[8 * q + 1]) * inv);
-            o4.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv);
-            o4.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv);
-            o4.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv);
-            *reinterpret_cast<uint4*>(op + c * 32 + q * 8) = o4;
-          }
-        }
-      }
-      if (row_ok) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S + q_idx] = m_used + log2f(l);   // base-2 log-sum-exp of the scaled scores
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem, 256);
-  }
-}
-
 // ================================================================================================ forward, P in TMEM
-// Same tiling as flash_fwd64_kernel, but the probabilities never touch shared memory: the softmax threads write P
-// (bf16) over the first 32 columns of the S buffer they just read and P·V runs with the A operand in tensor memory.
-// The two S buffers therefore double-buffer P as well, the wait for the previous P·V disappears from the softmax
-// loop (it is only needed on the rare O rescale), S is read from TMEM once, and the freed 16 KB hold a second V stage.
+// CTA = (128 query rows, head, batch); loops over 64-wide KV blocks up to the diagonal; S(j+1) = Q K^T is issued
+// before P(j) V so the tensor core overlaps the softmax; O stays in TMEM and is rescaled lazily (only when a row max
+// grows by > 2^8).  The probabilities never touch shared memory: the softmax threads write P (bf16) over the first 32
+// columns of the S buffer they just read and P·V runs with the A operand in tensor memory.  The two S buffers
+// therefore double-buffer P as well, the wait for the previous P·V is only needed on the rare O rescale, S is read
+// from TMEM once, and K and V each have two 16 KB stages.
 struct Fwd64TBars {
   uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done;
   uint32_t tmem_slot;
@@ -610,28 +400,17 @@ static AttnDev make_dev(const AttnArgs& a) {
   return p;
 }
 
-// HIMUON_ATTN_FWD=legacy keeps P in shared memory (flash_fwd64_kernel).
-static bool fwd_p_in_tmem() {
-  static const bool v = [] {
-    const char* e = getenv("HIMUON_ATTN_FWD");
-    return !(e && std::string(e) == "legacy");
-  }();
-  return v;
-}
-
 void flash_fwd_kv64(const AttnArgs& a, cudaStream_t s) {
   constexpr size_t SMEM = 1024 + TILE_BYTES + 3 * KV_TILE + P_BYTES + 256;
   static bool attr = false;
   if (!attr) {
-    cudaFuncSetAttribute(flash_fwd64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
     cudaFuncSetAttribute(flash_fwd64_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
     attr = true;
   }
   const AttnDev p = make_dev(a);
   const CUtensorMap tq = head_tmap(a.q, a.B, a.S, a.Hq, a.ld_q), tk = head_tmap(a.k, a.B, a.S, a.Hkv, a.ld_k, BKV),
                     tv = head_tmap(a.v, a.B, a.S, a.Hkv, a.ld_v, BKV);
-  if (fwd_p_in_tmem()) flash_fwd64_t_kernel<<<dim3(p.nblk, a.Hq, a.B), 192, SMEM, s>>>(tq, tk, tv, p);
-  else flash_fwd64_kernel<<<dim3(p.nblk, a.Hq, a.B), 192, SMEM, s>>>(tq, tk, tv, p);
+  flash_fwd64_t_kernel<<<dim3(p.nblk, a.Hq, a.B), 192, SMEM, s>>>(tq, tk, tv, p);
 }
 
 void flash_bwd_dq_kv64(const AttnArgs& a, cudaStream_t s) {

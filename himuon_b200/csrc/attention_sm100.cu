@@ -1,391 +1,18 @@
-// Causal grouped-query flash attention for head_dim 128 on sm_100a (forward and backward).
+// Causal grouped-query flash attention for head_dim 128 on sm_100a: the host entry points (flash_attn_fwd,
+// flash_attn_bwd) and the dK/dV kernel for sequence lengths that are not a multiple of 128.
 //
-// Every score / value product runs on tcgen05 tensor cores with TMEM accumulators; Q, K, V
-// and dO tiles arrive by TMA (128-byte swizzle, no multicast); probabilities and dS are
-// written by the softmax threads into swizzled shared memory and consumed as UMMA operands.
-// One thread owns one row of a 128-row tile, so row max / row sum need no shuffles.
+// Every score / value product runs on tcgen05 tensor cores with TMEM accumulators; Q, K, V and dO tiles arrive by
+// TMA (128-byte swizzle, no multicast).  One thread owns one row of a 128-row tile, so row max / row sum need no
+// shuffles.  Forward and the ragged-length dQ pass live in attention_kv64_sm100.cu, the pipelined backward kernels
+// (sequence lengths that are multiples of 128) in attention_bwd_sm100.cu.  The dK/dV kernel here: CTA = (KV block,
+// KV head or query head), loops over the query blocks at or below the diagonal, keeps dK and dV in TMEM, P and dS go
+// through swizzled shared memory; grouped heads need no atomics.
 //
-//   forward : CTA = (128 query rows, head, batch); loops over KV blocks up to the diagonal;
-//             S(j+1) = Q K^T is issued before P(j) V so the tensor core overlaps the softmax.
-//             O stays in TMEM and is rescaled lazily (only when a row max grows by > 2^8).
-//   backward: two kernels.  dq kernel: CTA = query block, loops KV blocks (also writes
-//             delta = rowsum(dO * O)).  dkv kernel: CTA = (KV block, KV head), loops over the
-//             query heads of its group and the query blocks at or below the diagonal, keeping
-//             dK and dV in TMEM, so grouped heads need no atomics.
-//
-// The reference reaches attention through HF `sdpa` (PyTorch library kernels); it ships no
-// attention code of its own.
+// The reference reaches attention through HF `sdpa` (PyTorch library kernels); it ships no attention code of its own.
 #include "attention_common.cuh"
 
-#include <cstdlib>
 
 namespace himuon {
-
-// ================================================================================================ forward
-__global__ void __launch_bounds__(192, 1)
-flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, AttnDev p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = align_up_1024(smem_raw);
-  uint8_t* sQ = smem;
-  uint8_t* sK = smem + TILE_BYTES;           // 2 stages
-  uint8_t* sV = smem + 3 * TILE_BYTES;       // 2 stages
-  uint8_t* sP = smem + 5 * TILE_BYTES;
-  AttnBars* bars = reinterpret_cast<AttnBars*>(smem + 6 * TILE_BYTES);
-  volatile int* abort_flag = &bars->abort_flag;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int sblk, h, b;
-  attn_block_coords(sblk, h, b);
-  const int qb = gridDim.x - 1 - sblk;         // heavy (late) query blocks first
-  const int hk = h / (p.Hq / p.Hkv);
-  const int nkv = qb + 1;
-
-  if (threadIdx.x == 0) {
-    mbar_init(&bars->q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->k_full[i], 1); mbar_init(&bars->v_full[i], 1);
-      mbar_init(&bars->k_empty[i], 1); mbar_init(&bars->v_empty[i], 1);
-      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_empty[i], 128);
-    }
-    mbar_init(&bars->p_ready, 128);
-    mbar_init(&bars->o_done, 1);
-    bars->abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 1) tmem_alloc(&bars->tmem_slot, 512);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = bars->tmem_slot;
-  const uint32_t tS0 = tmem, tO = tmem + 256;   // S buffers at columns 0 and 128, O at 256
-
-  if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(&bars->q_full, TILE_BYTES);
-      tma_load_4d(sQ, &tmQ, &bars->q_full, 0, h, qb * AT, b);
-      tma_load_4d(sQ + HALF_BYTES, &tmQ, &bars->q_full, 64, h, qb * AT, b);
-      for (int j = 0; j < nkv; ++j) {
-        const int st = j & 1;
-        const uint32_t par = ((j >> 1) & 1) ^ 1;
-        if (!mbar_wait(&bars->k_empty[st], par, abort_flag, p.status, 4)) break;
-        mbar_expect_tx(&bars->k_full[st], TILE_BYTES);
-        tma_load_4d(sK + st * TILE_BYTES, &tmK, &bars->k_full[st], 0, hk, j * AT, b);
-        tma_load_4d(sK + st * TILE_BYTES + HALF_BYTES, &tmK, &bars->k_full[st], 64, hk, j * AT, b);
-        if (!mbar_wait(&bars->v_empty[st], par, abort_flag, p.status, 4)) break;
-        mbar_expect_tx(&bars->v_full[st], TILE_BYTES);
-        tma_load_4d(sV + st * TILE_BYTES, &tmV, &bars->v_full[st], 0, hk, j * AT, b);
-        tma_load_4d(sV + st * TILE_BYTES + HALF_BYTES, &tmV, &bars->v_full[st], 64, hk, j * AT, b);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, false, true);
-      const uint32_t q_base = smem_u32(sQ), p_base = smem_u32(sP);
-      bool ok = mbar_wait(&bars->q_full, 0, abort_flag, p.status, 4);
-      auto issue_s = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!mbar_wait(&bars->k_full[st], (j >> 1) & 1, abort_flag, p.status, 4)) return false;
-        if (j >= 2 && !mbar_wait(&bars->s_empty[st], ((j >> 1) - 1) & 1, abort_flag, p.status, 4)) return false;
-        tc_fence_after();
-        const uint32_t k_base = smem_u32(sK + st * TILE_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ss(tS0 + st * 128, desc_kmajor(q_base, ks), desc_kmajor(k_base, ks), idesc_s, ks > 0 ? 1u : 0u);
-        umma_commit(&bars->k_empty[st]);
-        umma_commit(&bars->s_full[st]);
-        return true;
-      };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; ok && j < nkv; ++j) {
-        if (j + 1 < nkv) { ok = issue_s(j + 1); if (!ok) break; }
-        const int st = j & 1;
-        if (!mbar_wait(&bars->p_ready, j & 1, abort_flag, p.status, 4)) break;
-        if (!mbar_wait(&bars->v_full[st], (j >> 1) & 1, abort_flag, p.status, 4)) break;
-        tc_fence_after();
-        const uint32_t v_base = smem_u32(sV + st * TILE_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ss(tO, desc_kmajor(p_base, ks), desc_mnmajor(v_base, ks), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&bars->v_empty[st]);
-        umma_commit(&bars->o_done);
-      }
-    }
-  } else {
-    // ------------------------------------------------------------ softmax / epilogue: one thread per query row
-    const int row = (warp & 3) * 32 + lane;
-    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const int q_idx = qb * AT + row;
-    float m_used = -INFINITY, l = 0.f;
-    bool ok = true;
-    for (int j = 0; j < nkv; ++j) {
-      const int st = j & 1;
-      if (!mbar_wait(&bars->s_full[st], (j >> 1) & 1, abort_flag, p.status, 4)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t tS = tS0 + st * 128 + lane_off;
-      const bool diag = (j == qb);
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          float s = __uint_as_float(v[t]) * p.scale_log2;
-          if (diag && (c * 32 + t > row)) s = -INFINITY;
-          mx = fmaxf(mx, s);
-        }
-      }
-      const float m_new = fmaxf(m_used, mx);
-      // lazy rescale: keep the old reference max unless some row of this warp grew by more than 2^8
-      const bool need = (j > 0) && (m_new - m_used > 8.f);
-      const bool warp_need = __any_sync(0xffffffffu, need);
-      float alpha = 1.f;
-      if (j == 0) {
-        m_used = m_new;
-      } else if (warp_need) {
-        alpha = exp2f(m_used - m_new);
-        m_used = m_new;
-      }
-      if (j > 0) {
-        if (!mbar_wait(&bars->o_done, (j - 1) & 1, abort_flag, p.status, 4)) { ok = false; break; }
-        tc_fence_after();
-        if (warp_need) {
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t v[32];
-            tmem_ld32(tO + lane_off + c * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int t = 0; t < 32; ++t) v[t] = __float_as_uint(__uint_as_float(v[t]) * alpha);
-            tmem_st32(tO + lane_off + c * 32, v);
-          }
-          tmem_st_wait();
-          l *= alpha;
-        }
-      }
-      float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + c * 32, v);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int t = 0; t < 32; t += 2) {
-          float s0 = __uint_as_float(v[t]) * p.scale_log2 - m_used;
-          float s1 = __uint_as_float(v[t + 1]) * p.scale_log2 - m_used;
-          float p0 = exp2f(s0), p1 = exp2f(s1);
-          if (diag) {
-            if (c * 32 + t > row) p0 = 0.f;
-            if (c * 32 + t + 1 > row) p1 = 0.f;
-          }
-          pk[t >> 1] = pack_bf16x2(p0, p1);
-          // the row sum uses the rounded probabilities that the tensor core will see
-          rs += bf16_lo(pk[t >> 1]) + bf16_hi(pk[t >> 1]);
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          *reinterpret_cast<uint4*>(sP + sw128_off(row, c * 4 + q)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-      }
-      l += rs;
-      tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive(&bars->s_empty[st]);
-      mbar_arrive(&bars->p_ready);
-    }
-    if (ok && mbar_wait(&bars->o_done, (nkv - 1) & 1, abort_flag, p.status, 4)) {
-      tc_fence_after();
-      const float inv = 1.f / l;
-      const bool row_ok = q_idx < p.S;
-      __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.o) + (static_cast<long long>(b) * p.S + q_idx) * p.ld_o + h * HD;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tO + lane_off + c * 32, v);
-        tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 o4;
-            o4.x = pack_bf16x2(__uint_as_float(v[8 * q + 0]) * inv, __uint_as_float(v[8 * q + 1]) * inv);
-            o4.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv);
-            o4.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv);
-            o4.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv);
-            *reinterpret_cast<uint4*>(op + c * 32 + q * 8) = o4;
-          }
-        }
-      }
-      if (row_ok) p.lse[(static_cast<long long>(b) * p.Hq + h) * p.S + q_idx] = m_used + log2f(l);   // base-2 log-sum-exp of the scaled scores
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem, 512);
-  }
-}
-
-// ================================================================================================ backward: dQ
-// CTA = (query block, head, batch).  Resident: Q, dO.  Streamed: K_j, V_j.  TMEM: S | dP | dQ.
-__global__ void __launch_bounds__(192, 1)
-flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, AttnDev p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = align_up_1024(smem_raw);
-  uint8_t* sQ = smem;
-  uint8_t* sDO = smem + TILE_BYTES;
-  uint8_t* sK = smem + 2 * TILE_BYTES;
-  uint8_t* sV = smem + 3 * TILE_BYTES;
-  uint8_t* sDS = smem + 4 * TILE_BYTES;
-  BwdBars* bars = reinterpret_cast<BwdBars*>(smem + 5 * TILE_BYTES);
-  volatile int* abort_flag = &bars->abort_flag;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int sblk, h, b;
-  attn_block_coords(sblk, h, b);
-  const int qb = gridDim.x - 1 - sblk;         // heavy (late) query blocks first
-  const int hk = h / (p.Hq / p.Hkv);
-  const int nkv = qb + 1;
-
-  if (threadIdx.x == 0) {
-    mbar_init(&bars->a_full, 1); mbar_init(&bars->a_empty, 1);
-    mbar_init(&bars->b_full, 1); mbar_init(&bars->b_empty, 1);
-    mbar_init(&bars->sp_full, 1); mbar_init(&bars->ds_ready, 128); mbar_init(&bars->acc_done, 1);
-    bars->abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 1) tmem_alloc(&bars->tmem_slot, 512);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = bars->tmem_slot;
-  const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(&bars->a_full, 2 * TILE_BYTES);
-      tma_load_4d(sQ, &tmQ, &bars->a_full, 0, h, qb * AT, b);
-      tma_load_4d(sQ + HALF_BYTES, &tmQ, &bars->a_full, 64, h, qb * AT, b);
-      tma_load_4d(sDO, &tmDO, &bars->a_full, 0, h, qb * AT, b);
-      tma_load_4d(sDO + HALF_BYTES, &tmDO, &bars->a_full, 64, h, qb * AT, b);
-      for (int j = 0; j < nkv; ++j) {
-        if (!mbar_wait(&bars->b_empty, (j & 1) ^ 1, abort_flag, p.status, 4)) break;
-        mbar_expect_tx(&bars->b_full, 2 * TILE_BYTES);
-        tma_load_4d(sK, &tmK, &bars->b_full, 0, hk, j * AT, b);
-        tma_load_4d(sK + HALF_BYTES, &tmK, &bars->b_full, 64, hk, j * AT, b);
-        tma_load_4d(sV, &tmV, &bars->b_full, 0, hk, j * AT, b);
-        tma_load_4d(sV + HALF_BYTES, &tmV, &bars->b_full, 64, hk, j * AT, b);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_kmn = umma_idesc_bf16(128, 128, false, true);
-      const uint32_t q_base = smem_u32(sQ), do_base = smem_u32(sDO), k_base = smem_u32(sK), v_base = smem_u32(sV),
-                     ds_base = smem_u32(sDS);
-      bool ok = mbar_wait(&bars->a_full, 0, abort_flag, p.status, 4);
-      for (int j = 0; ok && j < nkv; ++j) {
-        if (!mbar_wait(&bars->b_full, j & 1, abort_flag, p.status, 4)) break;
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_ss(tS, desc_kmajor(q_base, ks), desc_kmajor(k_base, ks), idesc_kk, ks > 0 ? 1u : 0u);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_ss(tDP, desc_kmajor(do_base, ks), desc_kmajor(v_base, ks), idesc_kk, ks > 0 ? 1u : 0u);
-        umma_commit(&bars->sp_full);
-        if (!mbar_wait(&bars->ds_ready, j & 1, abort_flag, p.status, 4)) break;
-        tc_fence_after();
-        // dQ += dS K_j : A = dS (K-major over keys), B = K_j viewed MN-major (d contiguous)
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ss(tDQ, desc_kmajor(ds_base, ks), desc_mnmajor(k_base, ks), idesc_kmn, (j > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&bars->b_empty);
-        umma_commit(&bars->acc_done);
-      }
-    }
-  } else {
-    const int row = (warp & 3) * 32 + lane;
-    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const int q_idx = qb * AT + row;
-    const bool row_ok = q_idx < p.S;
-    const long long stat_idx = (static_cast<long long>(b) * p.Hq + h) * p.S + q_idx;
-    float lse2 = 0.f, delta = 0.f;
-    if (row_ok) {
-      lse2 = p.lse[stat_idx];
-      const __nv_bfloat16* op = reinterpret_cast<const __nv_bfloat16*>(p.o_in) + (static_cast<long long>(b) * p.S + q_idx) * p.ld_o + h * HD;
-      const __nv_bfloat16* gp = reinterpret_cast<const __nv_bfloat16*>(p.d_o) + (static_cast<long long>(b) * p.S + q_idx) * p.ld_do + h * HD;
-#pragma unroll 4
-      for (int c = 0; c < 16; ++c) {
-        const uint4 a = reinterpret_cast<const uint4*>(op)[c], g = reinterpret_cast<const uint4*>(gp)[c];
-        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) delta += bf16_lo(aw[q]) * bf16_lo(gw[q]) + bf16_hi(aw[q]) * bf16_hi(gw[q]);
-      }
-      p.delta[stat_idx] = delta;
-    }
-    bool ok = true;
-    for (int j = 0; j < nkv; ++j) {
-      if (!mbar_wait(&bars->sp_full, j & 1, abort_flag, p.status, 4)) { ok = false; break; }
-      tc_fence_after();
-      if (j > 0 && !mbar_wait(&bars->acc_done, (j - 1) & 1, abort_flag, p.status, 4)) { ok = false; break; }
-      const bool diag = (j == qb);
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld32(tS + lane_off + c * 32, sv);
-        tmem_ld32(tDP + lane_off + c * 32, dv);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int t = 0; t < 32; t += 2) {
-          float p0 = exp2f(__uint_as_float(sv[t]) * p.scale_log2 - lse2);
-          float p1 = exp2f(__uint_as_float(sv[t + 1]) * p.scale_log2 - lse2);
-          if (!row_ok || (diag && (c * 32 + t > row))) p0 = 0.f;
-          if (!row_ok || (diag && (c * 32 + t + 1 > row))) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(dv[t]) - delta) * p.scale;
-          const float d1 = p1 * (__uint_as_float(dv[t + 1]) - delta) * p.scale;
-          pk[t >> 1] = pack_bf16x2(d0, d1);
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          *reinterpret_cast<uint4*>(sDS + sw128_off(row, c * 4 + q)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-      }
-      tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive(&bars->ds_ready);
-    }
-    if (ok && mbar_wait(&bars->acc_done, (nkv - 1) & 1, abort_flag, p.status, 4)) {
-      tc_fence_after();
-      __nv_bfloat16* dqp = reinterpret_cast<__nv_bfloat16*>(p.dq) + (static_cast<long long>(b) * p.S + q_idx) * p.ld_dq + h * HD;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tDQ + lane_off + c * 32, v);
-        tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 o4;
-            o4.x = pack_bf16x2(__uint_as_float(v[8 * q + 0]), __uint_as_float(v[8 * q + 1]));
-            o4.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
-            o4.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
-            o4.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
-            *reinterpret_cast<uint4*>(dqp + c * 32 + q * 8) = o4;
-          }
-        }
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem, 512);
-  }
-}
 
 // ================================================================================================ backward: dK, dV
 // CTA = (KV block, KV head, batch).  Resident: K_j, V_j.  Streamed: Q_i, dO_i over (group head, query block).
@@ -563,36 +190,9 @@ static void check_attn(const AttnArgs& a) {
   if (a.ld_q % 8 || a.ld_k % 8 || a.ld_v % 8 || a.ld_o % 8) throw std::runtime_error("himuon attention: token strides must be multiples of 8");
 }
 
-// HIMUON_ATTN_KV=128 selects the one-CTA-per-SM kernels with 128-wide KV blocks for the forward and dQ passes
-// (default: the 64-wide, two-CTAs-per-SM kernels of attention_kv64_sm100.cu).
-static bool use_kv64() {
-  static const bool v = [] {
-    const char* e = getenv("HIMUON_ATTN_KV");
-    return !(e && std::string(e) == "128");
-  }();
-  return v;
-}
-
 void flash_attn_fwd(const AttnArgs& a, cudaStream_t s) {
   check_attn(a);
-  if (use_kv64()) {
-    flash_fwd_kv64(a, s);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) throw std::runtime_error(std::string("himuon flash_attn_fwd launch failed: ") + cudaGetErrorString(e));
-    return;
-  }
-  constexpr size_t SMEM = 1024 + 6 * TILE_BYTES + 512;
-  static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM); attr = true; }
-  AttnDev p{};
-  p.o = a.o; p.lse = a.lse; p.B = a.B; p.S = a.S; p.Hq = a.Hq; p.Hkv = a.Hkv; p.ld_o = a.ld_o;
-  p.nblk = (a.S + AT - 1) / AT;
-  p.scale = a.scale; p.scale_log2 = a.scale * kLog2e;
-  p.status = status_word_ptr();
-  const CUtensorMap tq = head_tmap(a.q, a.B, a.S, a.Hq, a.ld_q), tk = head_tmap(a.k, a.B, a.S, a.Hkv, a.ld_k),
-                    tv = head_tmap(a.v, a.B, a.S, a.Hkv, a.ld_v);
-  dim3 grid(p.nblk, a.Hq, a.B);
-  flash_fwd_kernel<<<grid, 192, SMEM, s>>>(tq, tk, tv, p);
+  flash_fwd_kv64(a, s);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) throw std::runtime_error(std::string("himuon flash_attn_fwd launch failed: ") + cudaGetErrorString(e));
 }
@@ -600,11 +200,9 @@ void flash_attn_fwd(const AttnArgs& a, cudaStream_t s) {
 void flash_attn_bwd(const AttnArgs& a, cudaStream_t s) {
   check_attn(a);
   if (a.ld_do % 8 || a.ld_dq % 8 || a.ld_dk % 8 || a.ld_dv % 8) throw std::runtime_error("himuon attention: gradient strides must be multiples of 8");
-  constexpr size_t SMEM_DQ = 1024 + 5 * TILE_BYTES + 512;
   constexpr size_t SMEM_DKV = 1024 + 6 * TILE_BYTES + 512;
   static bool attr = false;
   if (!attr) {
-    cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_DQ);
     cudaFuncSetAttribute(flash_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_DKV);
     attr = true;
   }
@@ -618,8 +216,7 @@ void flash_attn_bwd(const AttnArgs& a, cudaStream_t s) {
   const CUtensorMap tq = head_tmap(a.q, a.B, a.S, a.Hq, a.ld_q), tk = head_tmap(a.k, a.B, a.S, a.Hkv, a.ld_k),
                     tv = head_tmap(a.v, a.B, a.S, a.Hkv, a.ld_v), tdo = head_tmap(a.d_o, a.B, a.S, a.Hq, a.ld_do);
   if (flash_bwd_dq_t_supported(a)) flash_bwd_dq_t(a, p, s);
-  else if (use_kv64()) flash_bwd_dq_kv64(a, s);
-  else flash_bwd_dq_kernel<<<dim3(p.nblk, a.Hq, a.B), 192, SMEM_DQ, s>>>(tq, tk, tv, tdo, p);
+  else flash_bwd_dq_kv64(a, s);                       // sequence lengths that are not a multiple of 128
   const int G = a.Hq / a.Hkv;
   if (G > 1 && a.dk_part != nullptr && a.dv_part != nullptr) {
     // one CTA per (KV block, query head): G times more CTAs, balanced across the SMs; the per-head partial

@@ -16,7 +16,6 @@
 #include "sm100_common.cuh"
 #include "tma_host.h"
 
-#include <cstdlib>
 
 namespace himuon {
 
@@ -316,30 +315,6 @@ static float* pair_scratch() {
   return per_device[dev];
 }
 
-static bool pair_split_enabled() {
-  static const bool v = [] {
-    const char* e = getenv("HIMUON_GEMM_PAIR_SPLITK");
-    return !(e && std::string(e) == "0");
-  }();
-  return v;
-}
-
-static bool pair_stream_k_enabled() {
-  static const bool v = [] {
-    const char* e = getenv("HIMUON_GEMM_STREAMK");
-    return !(e && std::string(e) == "0");
-  }();
-  return v;
-}
-
-static bool pair_reduce_out_enabled() {
-  static const bool v = [] {
-    const char* e = getenv("HIMUON_GEMM_REDUCE_OUT");
-    return !(e && std::string(e) == "0");
-  }();
-  return v;
-}
-
 template <int STAGES, bool A_MN, bool B_MN>
 static void launch_gemm2(const GemmArgs& a, cudaStream_t stream) {
   constexpr uint32_t STAGE_BYTES = (BM + BNH) * BK * 2;
@@ -382,7 +357,7 @@ static void launch_gemm2(const GemmArgs& a, cudaStream_t stream) {
   p.kblocks = (a.K + BK - 1) / BK;
   p.tma_store = 1;
   p.nslices = 1;
-  p.reduce_out = (pair_reduce_out_enabled() && a.aux == a.C && a.beta == 1.f && !a.round_acc &&
+  p.reduce_out = (a.aux == a.C && a.beta == 1.f && !a.round_acc &&
                   a.ldaux == a.ldc && a.strideAux == a.strideC) ? 1 : 0;
   p.status = status_word_ptr();
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * a.batch;
@@ -412,9 +387,9 @@ static void launch_gemm2(const GemmArgs& a, cudaStream_t stream) {
   float* scratch = nullptr;
   // Accumulating fp32 outputs need no scratch to split a tile along K (every part just adds into C), so their work is
   // dealt out in equal contiguous (tile, k-block) ranges whenever whole tiles would not fill the last wave.
-  const bool want_stream = p.reduce_out && pair_stream_k_enabled() && total % cap != 0 && p.kblocks >= 8 &&
+  const bool want_stream = p.reduce_out && total % cap != 0 && p.kblocks >= 8 &&
                            total * p.kblocks >= 8LL * cap;
-  if (!want_stream && pair_split_enabled() && total > cap / 2 && rem > 0 && rem * 2 <= cap && rem <= kPairTailMax && p.kblocks >= 16 &&
+  if (!want_stream && total > cap / 2 && rem > 0 && rem * 2 <= cap && rem <= kPairTailMax && p.kblocks >= 16 &&
       (scratch = pair_scratch()) != nullptr) {
     int sl = cap / rem;
     if (sl > p.kblocks / 8) sl = p.kblocks / 8;

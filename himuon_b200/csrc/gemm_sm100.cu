@@ -15,7 +15,6 @@
 #include "sm100_common.cuh"
 #include "tma_host.h"
 
-#include <cstdlib>
 
 namespace himuon {
 
@@ -363,30 +362,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
-// Developer knobs read once from the environment: HIMUON_GEMM_EPILOGUE=direct, HIMUON_GEMM_BN=128|192|256,
-// HIMUON_GEMM_PAIR=0 (never use the CTA-pair kernel).
-struct GemmTuning { bool force_direct = false; bool no_pair = false; int force_bn = 0; };
-static const GemmTuning& tuning() {
-  static GemmTuning t = [] {
-    GemmTuning g;
-    const char* e = getenv("HIMUON_GEMM_EPILOGUE");
-    if (e && std::string(e) == "direct") g.force_direct = true;
-    const char* pr = getenv("HIMUON_GEMM_PAIR");
-    if (pr && std::string(pr) == "0") g.no_pair = true;
-    const char* b = getenv("HIMUON_GEMM_BN");
-    if (b) g.force_bn = atoi(b);
-    return g;
-  }();
-  return t;
-}
-
 // bf16 output with a bf16 aux tile that TMA can fetch (16-byte aligned base, rows and batches)
 static bool aux_tma_ok(const GemmArgs& a) {
-  static const bool enabled = [] {
-    const char* e = getenv("HIMUON_GEMM_AUX_TMA");
-    return !(e && std::string(e) == "0");
-  }();
-  return enabled && a.aux != nullptr && !a.out_fp32 && a.ldaux % 8 == 0 && (a.batch == 1 || a.strideAux % 8 == 0) &&
+  return a.aux != nullptr && !a.out_fp32 && a.ldaux % 8 == 0 && (a.batch == 1 || a.strideAux % 8 == 0) &&
          reinterpret_cast<uintptr_t>(a.aux) % 16 == 0 && a.ldc % 8 == 0 && (a.batch == 1 || a.strideC % 8 == 0) &&
          reinterpret_cast<uintptr_t>(a.C) % 16 == 0;
 }
@@ -432,7 +410,6 @@ static void launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   const int row_align = 16 / esz;
   p.tma_store = (a.ldc % row_align == 0) && (a.batch == 1 || a.strideC % row_align == 0) &&
                 (reinterpret_cast<uintptr_t>(a.C) % 16 == 0) ? 1 : 0;
-  if (tuning().force_direct) p.tma_store = 0;
   CUtensorMap tmC = tmA;
   if (p.tma_store) {
     const uint64_t dimsC[3] = {static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.M), static_cast<uint64_t>(a.batch)};
@@ -477,14 +454,13 @@ int num_sms() {
 void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if (a.M <= 0 || a.N <= 0 || a.batch <= 0) return;
   if (a.K <= 0) throw std::runtime_error("himuon gemm: K must be positive");
-  if (!tuning().no_pair && !tuning().force_direct && tuning().force_bn == 0 && gemm2_supported(a)) {
+  if (gemm2_supported(a)) {
     gemm2_bf16(a, stream);
     return;
   }
   // Tile width.  The main loop is bound by L2 -> shared-memory traffic, so the widest tile (highest arithmetic
   // intensity) wins even when it costs an extra partial wave; narrow tiles are only for narrow outputs.
-  int best_bn = a.N <= 128 ? 128 : (a.N <= 192 ? 192 : 256);
-  if (tuning().force_bn == 128 || tuning().force_bn == 192 || tuning().force_bn == 256) best_bn = tuning().force_bn;
+  const int best_bn = a.N <= 128 ? 128 : (a.N <= 192 ? 192 : 256);
   const int sel = (a.a_mn ? 2 : 0) | (a.b_mn ? 1 : 0);
 #define HM_LAUNCH(BN_, ST_)                                                        \
   switch (sel) {                                                                   \
@@ -493,7 +469,7 @@ void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     case 2: launch_gemm<BN_, ST_, true, false>(a, stream); break;                  \
     default: launch_gemm<BN_, ST_, true, true>(a, stream); break;                  \
   }
-  if (best_bn == 256 && !tuning().force_direct && aux_tma_ok(a)) {
+  if (best_bn == 256 && aux_tma_ok(a)) {
     switch (sel) {
       case 0: launch_gemm<256, 3, false, false, true>(a, stream); break;
       case 1: launch_gemm<256, 3, false, true, true>(a, stream); break;

@@ -17,6 +17,8 @@ extern "C" {
 //   dy, x : (rows, cols) bf16, contiguous      w : (cols) bf16      rstd : (rows) fp32 from the forward pass
 //   dx    : (rows, cols) bf16 output            dw : (cols) bf16 output (gradient of the weight)
 //   stream: a cudaStream_t (may be 0)
+// dy, x, w, dx and dw must be 16-byte aligned (the kernels use 16-byte accesses) and cols a multiple of 8; a call
+// that breaks either rule is refused with an error code before any kernel is launched.
 // The per-column fp32 sums that the ordinary entry point keeps in a caller-allocated buffer live in a
 // fixed 64 KiB array inside the library image (every GPU that loads the library holds it until
 // exit).  Returns 0 on success; on failure returns non-zero and himuon_noalloc_last_error() says why

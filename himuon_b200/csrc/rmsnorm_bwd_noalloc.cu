@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdint>
 #include <mutex>
 #include <string>
 
@@ -20,7 +21,8 @@ static __device__ __align__(256) float g_colsum_scratch[HIMUON_NOALLOC_MAX_COLS]
 thread_local std::string t_last_error;
 
 // Host code must not use g_colsum_scratch as a pointer: the name is only a host-side handle.  The
-// device address is looked up once per device, with that device current.
+// device address is looked up once per device, with that device current, and cached for the life of the process
+// (a cudaDeviceReset in between would leave the cached address stale; the library does not support that).
 float* scratch_address() {
   static float* per_device[64] = {nullptr};
   static std::mutex mu;
@@ -57,6 +59,17 @@ extern "C" int himuon_rmsnorm_bwd_noalloc(const void* dy, const void* x, const v
     return 3;
   }
   if (cols % 8) { t_last_error = "cols must be a multiple of 8"; return 4; }
+  // The kernels move 16 bytes per access.  Callers of this C symbol bypass the tensor checks of the Python
+  // bindings, so a misaligned pointer is refused here, on the host, before anything is launched.
+  const void* vec_ptrs[5] = {dy, x, w, dx, dw};
+  const char* vec_names[5] = {"dy", "x", "w", "dx", "dw"};
+  for (int i = 0; i < 5; ++i) {
+    if (reinterpret_cast<uintptr_t>(vec_ptrs[i]) % 16 != 0) {
+      t_last_error = std::string(vec_names[i]) + " must be 16-byte aligned";
+      return 9;
+    }
+  }
+  if (reinterpret_cast<uintptr_t>(rstd) % 4 != 0) { t_last_error = "rstd must be 4-byte aligned"; return 9; }
   float* scratch = scratch_address();
   if (scratch == nullptr) {
     if (t_last_error.empty()) t_last_error = "cannot resolve the scratch array on the current device";

@@ -43,7 +43,9 @@ def test_no_alloc_entry_point_matches_regular_path_twice():
 
     lib, fn = _lib()
     stream = torch.cuda.current_stream().cuda_stream
-    for seed, (rows, cols) in enumerate([(513, 2560), (300, 1024)]):
+    # two calls in a row with different shapes, then the kernel variants for wide rows (cols > 5120), the largest
+    # supported width, and a narrow call after a wide one (the scratch still holds the wide call's sums)
+    for seed, (rows, cols) in enumerate([(513, 2560), (300, 1024), (96, 8192), (40, 16384), (130, 512)]):
         torch.manual_seed(seed)
         x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
         w = (1 + 0.1 * torch.randn(cols, device="cuda")).bfloat16()
@@ -71,3 +73,19 @@ def test_no_alloc_entry_point_rejects_oversized_input():
     f = torch.zeros(8, device="cuda", dtype=torch.float32)
     rc = fn(t.data_ptr(), t.data_ptr(), t.data_ptr(), f.data_ptr(), t.data_ptr(), t.data_ptr(), 1, 16384 + 8, 0)
     assert rc != 0 and b"exceeds" in lib.himuon_noalloc_last_error()
+
+
+def test_no_alloc_entry_point_rejects_misaligned_pointers_on_the_host():
+    lib, fn = _lib()
+    rows, cols = 4, 64
+    x = torch.zeros(rows * cols + 8, device="cuda", dtype=torch.bfloat16)
+    f = torch.zeros(rows, device="cuda", dtype=torch.float32)
+    good = x.data_ptr()
+    bad = good + 2                        # one bf16 element off a 16-byte boundary
+    assert good % 16 == 0
+    for which in range(5):                # dy, x, w, dx, dw in turn
+        ptrs = [good] * 5
+        ptrs[which] = bad
+        rc = fn(ptrs[0], ptrs[1], ptrs[2], f.data_ptr(), ptrs[3], ptrs[4], rows, cols, 0)
+        assert rc != 0 and b"16-byte aligned" in lib.himuon_noalloc_last_error(), which
+    torch.cuda.synchronize()              # nothing was launched, the context is untouched
