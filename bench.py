@@ -55,6 +55,8 @@ def parse():
                    help="bank working copy: full gathered copy (default), two-slot staging ring, or peer reads")
     p.add_argument("--fsdp-grads", type=str, default="replicated", choices=["replicated", "sharded"],
                    help="bank gradient accumulation: full buffer per rank (default) or per-group reduce-scatter")
+    p.add_argument("--nvls", action="store_true",
+                   help="gradient reductions through the NVLink switch (multimem) instead of peer loads")
     p.add_argument("--no-step-graph", action="store_true",
                    help="run forward/backward eagerly instead of replaying the captured micro-batch CUDA graphs")
     p.add_argument("--engine", type=str, default="fsdp", choices=["fsdp", "ddp"],
@@ -146,10 +148,10 @@ def run_ours(args):
     if args.engine == "fsdp":
         weights = "peer" if args.peer_weights else args.fsdp_weights
         engine = ShardedEngine(model, use_banks=args.optimizer in ("himuon", "muon-fsdp", "adamw"), weights=weights,
-                               grads=args.fsdp_grads)
+                               grads=args.fsdp_grads, nvls=args.nvls)
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
-        engine = DataParallelEngine(model)
+        engine = DataParallelEngine(model, nvls=args.nvls)
     ns = argparse.Namespace(lr=LR if args.optimizer != "adamw" else 1e-3, weight_decay=WD, tile_size=args.tile, cuda_graph=True,
                             cuda_graph_warmup=1)
     optimizer = get_optimizer(args.optimizer, model, ns)
@@ -212,7 +214,7 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model, "global_batch": args.micro_batch * args.grad_acc * world,
                        "seq_len": args.seq_len, "micro_batch_per_gpu": args.micro_batch, "grad_acc": args.grad_acc,
-                       "parallelism": (f"fsdp-banks{world}" + (f" weights={engine.weights_mode} grads={engine.grads_mode}" if world > 1 else "")) if args.engine == "fsdp" else f"dp{world}",
+                       "parallelism": (f"fsdp-banks{world}" + (f" weights={engine.weights_mode} grads={engine.grads_mode}" + (" nvls" if engine.nvls else "") if world > 1 else "")) if args.engine == "fsdp" else f"dp{world}",
                        "optimizer": f"{args.optimizer} tile {args.tile}, lr {ns.lr}, wd {WD}, cuda graph",
                        "forward_backward": "eager" if args.no_step_graph else "micro-batch CUDA graphs (public Trainer option)",
                        "activation_checkpointing": checkpointing,

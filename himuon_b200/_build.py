@@ -24,7 +24,7 @@ CUDA_SOURCES = [
     "soap_kernels.cu",
     "rmsnorm_bwd_noalloc.cu",
 ]
-CPP_SOURCES = ["bindings.cpp", "symm.cpp"]
+CPP_SOURCES = ["bindings.cpp", "symm.cpp", "vmm.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -257,7 +257,8 @@ static void soap_moments(const at::Tensor& g, const at::Tensor& g_rot, at::Tenso
   HM_CHECK(g.is_contiguous() && g_rot.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "soap_moments: contiguous tensors");
   HM_CHECK(g.numel() == g_rot.numel() && g.numel() == m.numel() && g.numel() == v.numel() && g.numel() % 8 == 0,
            "soap_moments: equal element counts, multiples of 8");
-  for (const at::Tensor* t : {&g, &g_rot, &m, &v})
+  const at::Tensor* all4[4] = {&g, &g_rot, &m, &v};
+  for (const at::Tensor* t : all4)
     HM_CHECK(reinterpret_cast<uintptr_t>(t->data_ptr()) % 16 == 0, "soap_moments: 16-byte aligned tensors");
   const c10::cuda::CUDAGuard guard(g.device());
   himuon::soap_moments(g.data_ptr(), g_rot.data_ptr(), m.data_ptr(), v.data_ptr(), g.numel(), (float)b1, (float)b2, cur_stream());
@@ -267,7 +268,8 @@ static void soap_ratio(const at::Tensor& m_rot, const at::Tensor& v, at::Tensor&
   HM_CHECK(m_rot.is_contiguous() && v.is_contiguous() && out.is_contiguous(), "soap_ratio: contiguous tensors");
   HM_CHECK(m_rot.numel() == v.numel() && m_rot.numel() == out.numel() && m_rot.numel() % 8 == 0,
            "soap_ratio: equal element counts, multiples of 8");
-  for (const at::Tensor* t : {&m_rot, &v, &out})
+  const at::Tensor* all3[3] = {&m_rot, &v, &out};
+  for (const at::Tensor* t : all3)
     HM_CHECK(reinterpret_cast<uintptr_t>(t->data_ptr()) % 16 == 0, "soap_ratio: 16-byte aligned tensors");
   const c10::cuda::CUDAGuard guard(m_rot.device());
   himuon::soap_ratio(m_rot.data_ptr(), v.data_ptr(), out.data_ptr(), m_rot.numel(), (float)eps, cur_stream());

@@ -201,6 +201,113 @@ void allreduce_symm(const CommPeers& peers, const CommBufs& bufs, long long n_el
     allreduce_symm_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 512, 0, s>>>(peers, bufs, n_elems, scale, epoch_local);
 }
 
+// ------------------------------------------------------------------------------------------------ NVLS (multimem)
+// `mc` is the multicast address of the same region on every rank (memory created by cuMemCreate and bound to one
+// multicast object, see vmm.cpp).  A multimem.ld_reduce through it makes the NVLink switch read every rank's copy and
+// return the sum, so the reducing rank receives one copy's worth of bytes instead of world-1; a multimem.st makes the
+// switch write every rank's copy, so the broadcasting rank sends each byte once.
+template <typename T>
+__device__ __forceinline__ uint4 multimem_ld_reduce_add(const void* mc_addr) {
+  uint4 r;
+  if (sizeof(T) == 2)
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+  else
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+  return r;
+}
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               :: "l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+template <typename T>
+__device__ __forceinline__ uint4 scale_vec(const uint4& x, float scale) {
+  uint4 o;
+  if (sizeof(T) == 2) {
+    o.x = pack_bf16x2(bf16_lo(x.x) * scale, bf16_hi(x.x) * scale); o.y = pack_bf16x2(bf16_lo(x.y) * scale, bf16_hi(x.y) * scale);
+    o.z = pack_bf16x2(bf16_lo(x.z) * scale, bf16_hi(x.z) * scale); o.w = pack_bf16x2(bf16_lo(x.w) * scale, bf16_hi(x.w) * scale);
+  } else {
+    o.x = __float_as_uint(__uint_as_float(x.x) * scale); o.y = __float_as_uint(__uint_as_float(x.y) * scale);
+    o.z = __float_as_uint(__uint_as_float(x.z) * scale); o.w = __float_as_uint(__uint_as_float(x.w) * scale);
+  }
+  return o;
+}
+
+// Two-shot all-reduce through the switch: each rank reduces its 1/world slice with multimem.ld_reduce and writes the
+// result to every rank with multimem.st.  Same handshakes as the peer-pointer kernel.
+template <typename T>
+__global__ void __launch_bounds__(512)
+allreduce_nvls_kernel(CommPeers peers, char* mc, long long n_elems, float scale, int* epoch_local) {
+  __shared__ bool ok;
+  constexpr int VEC = 16 / sizeof(T);
+  if (!block_handshake(peers, blockIdx.x, epoch_local, 0, &ok)) return;
+  const long long n_vec = n_elems / VEC;
+  const long long per_rank = n_vec / peers.world;
+  const long long v0 = per_rank * peers.rank;
+  for (long long v = v0 + blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < v0 + per_rank;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4 sum = multimem_ld_reduce_add<T>(mc + v * 16);
+    multimem_st_v4(mc + v * 16, scale_vec<T>(sum, scale));
+  }
+  block_handshake(peers, blockIdx.x, epoch_local, 1, &ok);
+}
+
+void allreduce_nvls(const CommPeers& peers, void* mc_region, long long n_elems, int is_fp32, float scale, int* epoch_local,
+                    int max_blocks, cudaStream_t s) {
+  if (n_elems <= 0) return;
+  const int vec = is_fp32 ? 4 : 8;
+  if (n_elems % (static_cast<long long>(vec) * peers.world))
+    throw std::runtime_error("himuon allreduce: element count must be a multiple of (16 bytes * world size)");
+  const long long per_rank_vec = n_elems / vec / peers.world;
+  long long blocks = (per_rank_vec + 511) / 512;
+  const int cap = max_blocks > 0 ? max_blocks : num_sms();
+  if (blocks > cap) blocks = cap;
+  if (blocks > kCommMaxBlocks - 1) blocks = kCommMaxBlocks - 1;
+  if (blocks < 1) blocks = 1;
+  if (is_fp32)
+    allreduce_nvls_kernel<float><<<static_cast<int>(blocks), 512, 0, s>>>(peers, static_cast<char*>(mc_region), n_elems, scale, epoch_local);
+  else
+    allreduce_nvls_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 512, 0, s>>>(peers, static_cast<char*>(mc_region), n_elems, scale, epoch_local);
+}
+
+// out = beta * out + scale * (sum over ranks of the region behind `mc`), the sum taken by the switch.  The caller
+// orders this after the ranks' writes (a barrier) exactly as for reduce_replicas.
+template <typename T>
+__global__ void __launch_bounds__(512)
+reduce_nvls_kernel(const char* mc, T* __restrict__ out, long long n_elems, float scale, float beta) {
+  constexpr int VEC = 16 / sizeof(T);
+  const long long n_vec = n_elems / VEC;
+  for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < n_vec;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint4 o = scale_vec<T>(multimem_ld_reduce_add<T>(mc + v * 16), scale);
+    if (beta != 0.f) {
+      const uint4 x = scale_vec<T>(reinterpret_cast<const uint4*>(out)[v], beta);
+      if (sizeof(T) == 2) {
+        o.x = pack_bf16x2(bf16_lo(o.x) + bf16_lo(x.x), bf16_hi(o.x) + bf16_hi(x.x)); o.y = pack_bf16x2(bf16_lo(o.y) + bf16_lo(x.y), bf16_hi(o.y) + bf16_hi(x.y));
+        o.z = pack_bf16x2(bf16_lo(o.z) + bf16_lo(x.z), bf16_hi(o.z) + bf16_hi(x.z)); o.w = pack_bf16x2(bf16_lo(o.w) + bf16_lo(x.w), bf16_hi(o.w) + bf16_hi(x.w));
+      } else {
+        o.x = __float_as_uint(__uint_as_float(o.x) + __uint_as_float(x.x)); o.y = __float_as_uint(__uint_as_float(o.y) + __uint_as_float(x.y));
+        o.z = __float_as_uint(__uint_as_float(o.z) + __uint_as_float(x.z)); o.w = __float_as_uint(__uint_as_float(o.w) + __uint_as_float(x.w));
+      }
+    }
+    reinterpret_cast<uint4*>(out)[v] = o;
+  }
+}
+
+void reduce_nvls(const void* mc_region, void* out, long long n_elems, int is_fp32, float scale, float beta, cudaStream_t s) {
+  if (n_elems <= 0) return;
+  const int vec = is_fp32 ? 4 : 8;
+  if (n_elems % vec) throw std::runtime_error("himuon reduce_nvls: element count must be a multiple of 16 bytes");
+  long long blocks = (n_elems / vec + 511) / 512;
+  const long long cap = static_cast<long long>(num_sms()) * 2;
+  if (blocks > cap) blocks = cap;
+  if (is_fp32)
+    reduce_nvls_kernel<float><<<static_cast<int>(blocks), 512, 0, s>>>(static_cast<const char*>(mc_region), static_cast<float*>(out), n_elems, scale, beta);
+  else
+    reduce_nvls_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 512, 0, s>>>(static_cast<const char*>(mc_region), static_cast<__nv_bfloat16*>(out), n_elems, scale, beta);
+}
+
 // ------------------------------------------------------------------------------------------------ reduce replicas
 template <typename T>
 __global__ void __launch_bounds__(512)

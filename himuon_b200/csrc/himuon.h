@@ -170,6 +170,10 @@ void peer_barrier(const CommPeers& peers, int* epoch_local, cudaStream_t s);
 // algo 0: by size (one-shot up to 256 KiB, two-shot above), 1: one-shot (regions up to 2 MiB), 2: two-shot.
 void allreduce_symm(const CommPeers& peers, const CommBufs& bufs, long long n_elems, int is_fp32, float scale,
                     int* epoch_local, int max_blocks, cudaStream_t s, int algo = 0);
+// NVLS variants: `mc_region` is the multicast address of the region (all ranks' copies behind one address, vmm.cpp).
+void allreduce_nvls(const CommPeers& peers, void* mc_region, long long n_elems, int is_fp32, float scale, int* epoch_local,
+                    int max_blocks, cudaStream_t s);
+void reduce_nvls(const void* mc_region, void* out, long long n_elems, int is_fp32, float scale, float beta, cudaStream_t s);
 // out = beta * out + scale * sum of the n_src replicas.
 void reduce_replicas(const CommBufs& srcs, int n_src, void* out, long long n_elems, int is_fp32, float scale,
                      cudaStream_t s, float beta = 0.f);

@@ -53,7 +53,9 @@ static at::Tensor tensor_view(int64_t ptr, std::vector<int64_t> shape, const std
 
 class Comm {
  public:
-  Comm(int rank, int world, std::vector<int64_t> heap_ptrs, double timeout_s) : heaps_(std::move(heap_ptrs)) {
+  // mc_ptr: multicast address of the heap (0 when the heap is not bound to a multicast object)
+  Comm(int rank, int world, std::vector<int64_t> heap_ptrs, double timeout_s, int64_t mc_ptr)
+      : heaps_(std::move(heap_ptrs)), mc_(reinterpret_cast<char*>(mc_ptr)) {
     if (world < 1 || world > kMaxSrc || static_cast<int>(heaps_.size()) != world)
       throw std::runtime_error("himuon symm: world size must be 1..8 with one heap pointer per rank");
     peers_.world = world;
@@ -77,16 +79,28 @@ class Comm {
   void allreduce(int64_t offset_bytes, int64_t n_elems, bool fp32, double scale, int64_t max_blocks, int64_t algo) {
     if (peers_.world == 1) return;
     TORCH_CHECK(offset_bytes % 16 == 0, "himuon allreduce: the region must start on a 16-byte boundary");
+    if (algo == 3) {                                   // through the NVLink switch (multimem)
+      TORCH_CHECK(mc_ != nullptr, "himuon allreduce: this heap has no multicast mapping");
+      allreduce_nvls(peers_, mc_ + offset_bytes, n_elems, fp32 ? 1 : 0, static_cast<float>(scale), epoch_,
+                     static_cast<int>(max_blocks), at::cuda::getCurrentCUDAStream().stream());
+      return;
+    }
     CommBufs b{};
     for (int r = 0; r < peers_.world; ++r) b.ptr[r] = reinterpret_cast<char*>(heaps_[r]) + offset_bytes;
     allreduce_symm(peers_, b, n_elems, fp32 ? 1 : 0, static_cast<float>(scale), epoch_, static_cast<int>(max_blocks),
                    at::cuda::getCurrentCUDAStream().stream(), static_cast<int>(algo));
   }
   // out = beta * out + scale * sum over ranks of the heap region at offset_bytes (out.numel() elements of out's dtype).
-  void reduce_to(int64_t offset_bytes, at::Tensor out, double scale, double beta) {
+  void reduce_to(int64_t offset_bytes, at::Tensor out, double scale, double beta, bool multicast) {
     TORCH_CHECK(out.is_cuda() && out.is_contiguous(), "himuon reduce_to: contiguous CUDA output expected");
     TORCH_CHECK(offset_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0,
                 "himuon reduce_to: 16-byte aligned regions expected");
+    if (multicast && peers_.world > 1) {
+      TORCH_CHECK(mc_ != nullptr, "himuon reduce_to: this heap has no multicast mapping");
+      reduce_nvls(mc_ + offset_bytes, out.data_ptr(), out.numel(), out.scalar_type() == at::kFloat ? 1 : 0,
+                  static_cast<float>(scale), static_cast<float>(beta), at::cuda::getCurrentCUDAStream().stream());
+      return;
+    }
     CommBufs b{};
     for (int r = 0; r < peers_.world; ++r) b.ptr[r] = reinterpret_cast<char*>(heaps_[r]) + offset_bytes;
     reduce_replicas(b, peers_.world, out.data_ptr(), out.numel(), out.scalar_type() == at::kFloat ? 1 : 0,
@@ -100,11 +114,15 @@ class Comm {
 
  private:
   std::vector<int64_t> heaps_;
+  char* mc_ = nullptr;
   CommPeers peers_{};
   int* epoch_ = nullptr;
 };
 
+void bind_vmm(py::module_& m);
+
 void bind_symm(py::module_& m) {
+  bind_vmm(m);
   m.def("symm_alloc", &symm_alloc);
   m.def("symm_open", &symm_open);
   m.def("symm_close", &symm_close);
@@ -112,14 +130,16 @@ void bind_symm(py::module_& m) {
   m.def("tensor_view", &tensor_view);
   m.def("multi_copy_units", [](int64_t bytes) { return multi_copy_units(bytes); });
   py::class_<Comm>(m, "Comm")
-      .def(py::init<int, int, std::vector<int64_t>, double>())
+      .def(py::init<int, int, std::vector<int64_t>, double, int64_t>(), py::arg("rank"), py::arg("world"), py::arg("heap_ptrs"),
+           py::arg("timeout_s"), py::arg("mc_ptr") = 0)
       .def("set_timeout", &Comm::set_timeout)
       .def("peer_ptr", &Comm::peer_ptr)
       .def_static("flag_bytes", &Comm::flag_bytes)
       .def("barrier", &Comm::barrier)
       .def("allreduce", &Comm::allreduce, py::arg("offset_bytes"), py::arg("n_elems"), py::arg("fp32"), py::arg("scale"),
            py::arg("max_blocks") = 0, py::arg("algo") = 0)
-      .def("reduce_to", &Comm::reduce_to, py::arg("offset_bytes"), py::arg("out"), py::arg("scale"), py::arg("beta") = 0.0)
+      .def("reduce_to", &Comm::reduce_to, py::arg("offset_bytes"), py::arg("out"), py::arg("scale"), py::arg("beta") = 0.0,
+           py::arg("multicast") = false)
       .def("copy_segments", &Comm::copy_segments);
 }
 

@@ -27,10 +27,11 @@ _LAYER_RE = re.compile(r"(?:^|\.)layers\.(\d+)\.")
 
 class DataParallelEngine:
     def __init__(self, model: torch.nn.Module, timeout_s: float = 120.0, broadcast_params: bool = True,
-                 overlap: bool = True, bucket_layers: int = 4, comm_blocks: int = 16):
+                 overlap: bool = True, bucket_layers: int = 4, comm_blocks: int = 16, nvls: bool = False):
         """``overlap``: start each bucket's all-reduce from inside the backward pass (side stream);
         ``bucket_layers``: decoder layers per bucket; ``comm_blocks``: grid cap of the overlapped all-reduce launches
-        (they share the SMs with the backward GEMMs)."""
+        (they share the SMs with the backward GEMMs); ``nvls``: bind the gradient heap to an NVLink multicast object
+        and reduce / broadcast through the switch (``multimem``) instead of peer loads and stores."""
         self.model = model
         self.rank, self.world = _world()
         named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
@@ -61,7 +62,8 @@ class DataParallelEngine:
                     for k in range(self.n_buckets))
             n += self._padded(sum(p.numel() for p in rec["rest"]))
             total += n * esz + 4096
-        self.heap = SymmetricHeap(total, self.device, timeout_s)
+        self.heap = SymmetricHeap(total, self.device, timeout_s, multicast=nvls)
+        self._algo = 3 if self.heap.has_multicast else 0
         self.regions = []          # (flat tensor, heap offset) per dtype: zeroing and whole-region reduction
         self.buckets: list[list] = [[] for _ in range(self.n_buckets)]   # per bucket: (slice, heap offset) per dtype
         self.rest = []             # (slice, heap offset) per dtype
@@ -102,6 +104,13 @@ class DataParallelEngine:
         self.overlapped_launches = 0
         object.__setattr__(model, "_layer_hooks", self if self.overlap else None)
 
+    def _region_algo(self, flat) -> int:
+        """Through the switch when the heap has a multicast mapping, except for regions small enough for the
+        latency-bound one-shot kernel."""
+        if self._algo == 3 and flat.numel() * flat.element_size() > (256 << 10):
+            return 3
+        return 0
+
     def _bucket_range(self, k: int):
         return range(k * self.bucket_layers, min(self.n_layers, (k + 1) * self.bucket_layers))
 
@@ -129,7 +138,7 @@ class DataParallelEngine:
         self.overlapped_launches += 1
         if not self.cuda:
             for flat, offset in self.buckets[k]:
-                self.heap.allreduce_(flat, offset, 1.0 / self.world)
+                self.heap.allreduce_(flat, offset, 1.0 / self.world, algo=self._region_algo(flat))
             return
         main = torch.cuda.current_stream(self.device)
         ready = torch.cuda.Event()
@@ -137,7 +146,7 @@ class DataParallelEngine:
         with torch.cuda.stream(self._side):
             self._side.wait_event(ready)
             for flat, offset in self.buckets[k]:
-                self.heap.allreduce_(flat, offset, 1.0 / self.world, max_blocks=self.comm_blocks)
+                self.heap.allreduce_(flat, offset, 1.0 / self.world, max_blocks=self.comm_blocks, algo=self._algo)
             done = torch.cuda.Event()
             done.record(self._side)
         if k == 0:
@@ -173,14 +182,14 @@ class DataParallelEngine:
             self._side_done = None
         if not self._launched:                       # nothing was overlapped: one launch per dtype region
             for flat, offset in self.regions:
-                self.heap.allreduce_(flat, offset, 1.0 / self.world)
+                self.heap.allreduce_(flat, offset, 1.0 / self.world, algo=self._region_algo(flat))
             return
         for k in range(self.n_buckets):
             if k not in self._launched:
                 for flat, offset in self.buckets[k]:
-                    self.heap.allreduce_(flat, offset, 1.0 / self.world)
+                    self.heap.allreduce_(flat, offset, 1.0 / self.world, algo=self._region_algo(flat))
         for flat, offset in self.rest:
-            self.heap.allreduce_(flat, offset, 1.0 / self.world)
+            self.heap.allreduce_(flat, offset, 1.0 / self.world, algo=self._region_algo(flat))
         self._launched.clear()
 
     def zero_grad(self, set_to_none: bool = False):

@@ -63,9 +63,12 @@ class _BankState:
 class ShardedEngine:
     def __init__(self, model: nn.Module, use_banks: bool = True, cpu_offload: bool = False, timeout_s: float = 120.0,
                  gather_blocks: int = 0, peer_weights: bool = False, weights: str | None = None,
-                 grads: str = "replicated"):
+                 grads: str = "replicated", nvls: bool = False):
         """``weights``: ``"gathered"`` (default), ``"ring"`` or ``"peer"`` (``peer_weights=True`` is the older spelling
         of the last); ``grads``: ``"replicated"`` (default) or ``"sharded"``; see the module docstring.
+        ``nvls``: bind the symmetric heap to an NVLink multicast object; the gradient reductions onto the owners then
+        read through it (``multimem.ld_reduce``: the switch sums the ranks' copies, the owner receives one copy's worth
+        of bytes instead of ``world - 1``) and the replicated parameters' all-reduce goes through the switch too.
         ``cpu_offload``: keep the optimizer's state tensors in pinned host memory between steps (see
         :class:`OptimizerStateOffload`; the reference's ``--cpu-offload``, ``train_fsdp.py:58,120``)."""
         self.model = model
@@ -108,7 +111,8 @@ class ShardedEngine:
             slots = n_local                                            # the owned shard
             slots += n_local * self.world if grads == "replicated" else unit * self.world   # gradient buffer
             need += slots * H * W * esz + 16384
-        self.heap = SymmetricHeap(need, self.device, timeout_s)
+        self.heap = SymmetricHeap(need, self.device, timeout_s, multicast=nvls)
+        self.nvls = self.heap.has_multicast
 
         # ---- replicated parameters: gradients in one flat symmetric region per dtype
         self.regions = []
@@ -265,7 +269,9 @@ class ShardedEngine:
         ``.grad`` on the bank shards.  With ``cpu_offload`` the optimizer's ``step`` is wrapped so that its state
         lives in pinned host memory between steps."""
         from ..optimizers import HiMuon
-        fused = isinstance(optimizer, HiMuon) and self.cuda and self.grads_mode == "replicated"
+        # with a multicast heap the replicas are summed by the switch in one reduce launch per bank instead of by peer
+        # loads inside momentum_tile
+        fused = isinstance(optimizer, HiMuon) and self.cuda and self.grads_mode == "replicated" and not self.nvls
         self.materialize_grads = not fused and self.grads_mode == "replicated"
         if not fused:
             for st in self.state.values():
@@ -423,7 +429,7 @@ class ShardedEngine:
             H, W = st.spec.matrix_shape
             esz = st.shard.element_size()
             off = st.gring_off + self.rank * st.unit * H * W * esz
-            self.heap.comm.reduce_to(off, st.grad_shard[g * st.unit:(g + 1) * st.unit], scale, 1.0)
+            self.heap.comm.reduce_to(off, st.grad_shard[g * st.unit:(g + 1) * st.unit], scale, 1.0, self.nvls)
             ops._count()
         self.heap.barrier()
         ops._count()
@@ -440,7 +446,8 @@ class ShardedEngine:
                     st.param.grad = st.grad_full
             return
         for flat, offset in self.regions:          # also orders this rank after every peer's backward
-            self.heap.allreduce_(flat, offset, 1.0 / self.world)
+            big = flat.numel() * flat.element_size() > (256 << 10)
+            self.heap.allreduce_(flat, offset, 1.0 / self.world, algo=3 if (self.nvls and big) else 0)
         if not self.regions:
             self.heap.barrier()
         if not self.materialize_grads:
@@ -452,7 +459,7 @@ class ShardedEngine:
                 st.param.grad = torch.empty_like(st.shard)
             if self.cuda:
                 esz = st.shard.element_size()
-                self.heap.comm.reduce_to(st.grad_off + lo * H * W * esz, st.param.grad, 1.0 / self.world, 0.0)
+                self.heap.comm.reduce_to(st.grad_off + lo * H * W * esz, st.param.grad, 1.0 / self.world, 0.0, self.nvls)
                 ops._count()
             else:
                 work = st.grad_full.float()

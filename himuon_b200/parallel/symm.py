@@ -5,6 +5,14 @@ opens the peers' handles, after which any rank can address any other rank's heap
 loads and stores over NVLink.  Every rank allocates the same sequence of regions, so a region is
 identified by its byte offset and ``peer_view(r, ...)`` returns rank ``r``'s copy of it.
 
+With ``multicast=True`` the heap is created with the CUDA virtual-memory API instead (``csrc/vmm.cpp``) and every
+rank's memory is also bound to one NVLink multicast object: ``multimem`` loads through the multicast address are
+reduced inside the NVLink switch and ``multimem`` stores are replicated by it (NVLS), which the all-reduce
+(``algo=3``) and ``reduce_to(multicast=True)`` kernels use.  Where the device or the setup does not support it the
+heap falls back to the IPC kind on every rank together.  A rank must not exit while its memory is bound to the
+multicast object and peers may still touch it: ``close()`` synchronises, meets the other ranks at a barrier and only
+then unbinds and unmaps.
+
 The first bytes of the heap hold the flag area used by the kernels' bounded-wait handshakes.
 On CPU (gloo) runs the heap is ordinary host memory and the collectives fall back to
 ``torch.distributed`` calls, which keeps the engines' host-side logic testable without a GPU.
@@ -12,6 +20,9 @@ The reference has no counterpart: it delegates all communication to NCCL through
 """
 
 from __future__ import annotations
+
+import os
+import warnings
 
 import torch
 import torch.distributed as dist
@@ -27,8 +38,10 @@ def _world():
 
 
 class SymmetricHeap:
-    def __init__(self, nbytes: int, device: torch.device, timeout_s: float = 120.0):
+    def __init__(self, nbytes: int, device: torch.device, timeout_s: float = 120.0, multicast: bool = False):
         self.rank, self.world = _world()
+        self.has_multicast = False
+        self._vmm = False
         self.device = torch.device(device)
         self.cuda = self.device.type == "cuda"
         self.cursor = 0
@@ -43,21 +56,25 @@ class SymmetricHeap:
             self.flag_bytes = -(-flag_bytes // _ALIGN) * _ALIGN
             self.nbytes = self.flag_bytes + -(-int(nbytes) // _ALIGN) * _ALIGN + _ALIGN
             torch.cuda.set_device(self.device)
-            ptr, handle = self._ext.symm_alloc(self.nbytes)
-            self._own_ptr = ptr
-            self.ptrs = [ptr]
-            if self.world > 1:
-                handles = [None] * self.world
-                dist.all_gather_object(handles, handle)
-                self.ptrs = []
-                for r, h in enumerate(handles):
-                    if r == self.rank:
-                        self.ptrs.append(ptr)
-                    else:
-                        p = self._ext.symm_open(h)
-                        self._opened.append(p)
-                        self.ptrs.append(p)
-            self.comm = self._ext.Comm(self.rank, self.world, self.ptrs, float(timeout_s))
+            mc_ptr = 0
+            if multicast and self.world > 1:
+                mc_ptr = self._setup_multicast()
+            if not self._vmm:
+                ptr, handle = self._ext.symm_alloc(self.nbytes)
+                self._own_ptr = ptr
+                self.ptrs = [ptr]
+                if self.world > 1:
+                    handles = [None] * self.world
+                    dist.all_gather_object(handles, handle)
+                    self.ptrs = []
+                    for r, h in enumerate(handles):
+                        if r == self.rank:
+                            self.ptrs.append(ptr)
+                        else:
+                            p = self._ext.symm_open(h)
+                            self._opened.append(p)
+                            self.ptrs.append(p)
+            self.comm = self._ext.Comm(self.rank, self.world, self.ptrs, float(timeout_s), int(mc_ptr))
             self.cursor = self.flag_bytes
             if self.world > 1:
                 dist.barrier()
@@ -65,6 +82,78 @@ class SymmetricHeap:
             self.flag_bytes = 0
             self.nbytes = -(-int(nbytes) // _ALIGN) * _ALIGN + _ALIGN
             self._host = torch.zeros(self.nbytes, dtype=torch.uint8)
+
+    # ------------------------------------------------------------------ NVLS setup
+    def _setup_multicast(self) -> int:
+        """cuMemCreate'd heap, peers mapped through exchanged descriptors, everything bound to one multicast object.
+        Returns the multicast address, or 0 after falling back (all ranks take the same decision)."""
+        e, dev = self._ext, self.device.index or 0
+        ok = bool(e.vmm_multicast_supported(dev))
+        votes = [None] * self.world
+        dist.all_gather_object(votes, ok)
+        if not all(votes):
+            if self.rank == 0:
+                warnings.warn("SymmetricHeap: NVLink multicast is not supported here; using the IPC heap")
+            return 0
+        # Stages end with a vote so that a failure on one rank makes every rank fall back at the same point instead of
+        # leaving the others waiting in a collective.
+        st: dict = {}
+
+        def vote(stage_fn) -> bool:
+            err = None
+            try:
+                stage_fn()
+            except Exception as ex:              # noqa: BLE001 - any failure means: fall back, on every rank
+                err = f"{type(ex).__name__}: {ex}"
+            errs = [None] * self.world
+            dist.all_gather_object(errs, err)
+            bad = [x for x in errs if x is not None]
+            if bad:
+                st["error"] = bad[0]
+            return not bad
+
+        def stage_alloc():
+            st["size"] = int(e.vmm_round_size(self.nbytes, dev, self.world))
+            st["idx"], st["ptr"], st["fd"] = e.vmm_alloc(st["size"], dev)
+
+        def stage_import():
+            infos = [None] * self.world
+            dist.all_gather_object(infos, (os.getpid(), int(st["fd"])))
+            st["ptrs"] = [st["ptr"] if r == self.rank else int(e.vmm_import(pid, rfd, st["size"], dev))
+                          for r, (pid, rfd) in enumerate(infos)]
+
+        def stage_mc_create():
+            if self.rank == 0:
+                st["mc"], st["mc_fd"] = e.mc_create(self.world, st["size"], dev)
+
+        def stage_mc_import():
+            box = [(os.getpid(), int(st["mc_fd"]))] if self.rank == 0 else [None]
+            dist.broadcast_object_list(box, src=0)
+            if self.rank != 0:
+                st["mc"] = e.mc_import(box[0][0], box[0][1], st["size"], dev)
+            e.mc_add_device(st["mc"], dev)
+
+        def stage_bind():                        # runs after every device has been added (the vote is the barrier)
+            e.mc_bind(st["mc"], st["idx"])
+
+        def stage_map():                         # runs after every rank's memory has been bound
+            st["mc_ptr"] = int(e.mc_map(st["mc"]))
+
+        ok = all(vote(f) for f in (stage_alloc, stage_import, stage_mc_create, stage_mc_import, stage_bind, stage_map))
+        if not ok:
+            torch.cuda.synchronize(self.device)
+            dist.barrier()
+            e.vmm_release_all()
+            if self.rank == 0:
+                warnings.warn(f"SymmetricHeap: multicast setup failed ({st.get('error')}); using the IPC heap")
+            return 0
+        size, ptrs, mc_ptr = st["size"], st["ptrs"], st["mc_ptr"]
+        self.nbytes = size
+        self.ptrs = ptrs
+        self._own_ptr = 0
+        self._vmm = True
+        self.has_multicast = True
+        return mc_ptr
 
     # ------------------------------------------------------------------ allocation
     def alloc(self, shape, dtype) -> tuple[torch.Tensor, int]:
@@ -103,8 +192,9 @@ class SymmetricHeap:
 
     def allreduce_(self, tensor: torch.Tensor, offset: int, scale: float, max_blocks: int = 0, algo: int = 0):
         """In-place sum over ranks of the region ``tensor`` (at ``offset``) times ``scale``.  ``algo``: 0 picks the
-        one-shot kernel up to 256 KiB and the two-shot kernel above, 1 / 2 force one of them; ``max_blocks`` caps the
-        two-shot grid (a small grid leaves the SMs to a compute stream that runs beside it)."""
+        one-shot kernel up to 256 KiB and the two-shot kernel above, 1 / 2 force one of them, 3 reduces and broadcasts
+        through the NVLink switch (needs a multicast heap); ``max_blocks`` caps the two-shot grid (a small grid
+        leaves the SMs to a compute stream that runs beside it)."""
         if self.world == 1:
             if scale != 1.0:
                 tensor.mul_(scale)
@@ -129,6 +219,12 @@ class SymmetricHeap:
             if self.world > 1 and dist.is_initialized():
                 dist.barrier()
             self.comm = None
+            if self._vmm:
+                # all ranks are idle and past the barrier: nobody touches the multicast object any more
+                self._ext.vmm_release_all()
+                self._vmm = self.has_multicast = False
+                if self.world > 1 and dist.is_initialized():
+                    dist.barrier()
             for p in self._opened:
                 self._ext.symm_close(p)
             self._opened = []

@@ -67,6 +67,8 @@ def build_arg_parser(mode: str) -> argparse.ArgumentParser:
                    help="parameter dtype (default: bf16 on CUDA, fp32 on CPU)")
     p.add_argument("--device", type=str, default=None)
     if mode in ("ddp", "fsdp"):
+        p.add_argument("--nvls", action="store_true",
+                       help="bind the gradient heap to an NVLink multicast object and reduce through the switch (multimem)")
         p.add_argument("--time-stats", action="store_true")
         p.add_argument("--gradient-checkpointing", dest="gradient_checkpointing",
                        action=argparse.BooleanOptionalAction, default=True)
@@ -381,7 +383,7 @@ def run_training(args, mode: str) -> dict:
     engine, banks = None, None
     if mode == "ddp":
         from .parallel.ddp import DataParallelEngine
-        engine = DataParallelEngine(model)
+        engine = DataParallelEngine(model, nvls=bool(getattr(args, "nvls", False)))
     elif mode == "fsdp":
         from .parallel.fsdp import ShardedEngine
         # Banks (whole matrices sharded on the layer axis) serve every optimizer that updates a stacked (n, H, W)
@@ -393,7 +395,8 @@ def run_training(args, mode: str) -> dict:
             log(f"optimizer {opt_name!r} needs per-matrix parameters: parameters are replicated, not sharded")
         weights = "peer" if getattr(args, "peer_weights", False) else getattr(args, "fsdp_weights", "gathered")
         engine = ShardedEngine(model, use_banks=use_banks, cpu_offload=getattr(args, "cpu_offload", False),
-                               weights=weights, grads=getattr(args, "fsdp_grads", "replicated"))
+                               weights=weights, grads=getattr(args, "fsdp_grads", "replicated"),
+                               nvls=bool(getattr(args, "nvls", False)))
         banks = engine.banks
 
     tokens_per_step = args.batch_size * args.max_length * args.gradient_accumulation_steps * world_size

@@ -60,6 +60,8 @@ def main():
     ap.add_argument("--iters", type=int, default=7)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--nccl", action="store_true")
+    ap.add_argument("--nvls", action="store_true", help="bind the heap to an NVLink multicast object and also time the "
+                    "multimem variants (all-reduce through the switch, switch-side reduce)")
     ap.add_argument("--json", type=str, default=None)
     args = ap.parse_args()
 
@@ -73,7 +75,9 @@ def main():
     from himuon_b200.parallel.symm import SymmetricHeap
 
     max_bytes = args.max_mb << 20
-    heap = SymmetricHeap(2 * max_bytes + (64 << 20), device, timeout_s=30.0)
+    heap = SymmetricHeap(2 * max_bytes + (64 << 20), device, timeout_s=30.0, multicast=args.nvls)
+    if args.nvls and rank == 0:
+        print(f"# multicast heap: {heap.has_multicast}", flush=True)
     flush = torch.zeros(160 << 20, device=device, dtype=torch.float32)      # 640 MB > 126 MB L2
     rows = []
 
@@ -106,6 +110,9 @@ def main():
         if nbytes <= (1 << 20):
             ms = _time(lambda: heap.allreduce_(buf[:n], off, 1.0 / world, algo=2), args.iters, args.warmup, fl)
             report("allreduce_twoshot_forced", n * 2, ms, ar_factor * n * 2)
+        if heap.has_multicast and nbytes >= (1 << 20):
+            ms = _time(lambda: heap.allreduce_(buf[:n], off, 1.0 / world, algo=3), args.iters, args.warmup, fl)
+            report("allreduce_nvls", n * 2, ms, ar_factor * n * 2)
         if args.nccl:
             t = buf[:n]
             ms = _time(lambda: dist.all_reduce(t), args.iters, args.warmup, fl)
@@ -145,6 +152,9 @@ def main():
     out = torch.empty(shard_bytes // 2, device=device, dtype=torch.bfloat16)
     ms = _time(lambda: heap.comm.reduce_to(soff, out, 1.0 / world, 0.0), args.iters, args.warmup, None)
     report("reduce_scatter(reduce_to)", shard_bytes * world, ms, shard_bytes * (world - 1))
+    if heap.has_multicast:       # the switch sums the copies: this rank receives one copy's worth of bytes
+        ms = _time(lambda: heap.comm.reduce_to(soff, out, 1.0 / world, 0.0, True), args.iters, args.warmup, None)
+        report("reduce_scatter_nvls", shard_bytes * world, ms, shard_bytes)
     if args.nccl:
         full = gathered.view(-1)
         ms = _time(lambda: dist.reduce_scatter_tensor(out, full), args.iters, args.warmup, None)

@@ -30,22 +30,40 @@ def _batches(rank, steps, grad_acc, device):
     return out
 
 
-def scenario_collectives(device):
+def scenario_collectives(device, multicast=False):
     from himuon_b200 import ops
     from himuon_b200.parallel.symm import SymmetricHeap
 
     rank, world = dist.get_rank(), dist.get_world_size()
-    heap = SymmetricHeap(64 << 20, device, timeout_s=20.0)
-    for dtype, n in ((torch.bfloat16, 16 * world * 4099), (torch.float32, 16 * world * 513)):
+    heap = SymmetricHeap(64 << 20, device, timeout_s=20.0, multicast=multicast)
+    if multicast and not heap.has_multicast:
+        if rank == 0:
+            print("COLLECTIVES OK (no multicast support on this machine: IPC heap used)", flush=True)
+    # every algorithm on a small and a large region of both dtypes: 0 = by size, 1 = one-shot, 2 = two-shot,
+    # 3 = through the NVLink switch (multicast heaps only)
+    algos = [0, 1, 2] + ([3] if heap.has_multicast else [])
+    for dtype, n in ((torch.bfloat16, 16 * world * 4099), (torch.float32, 16 * world * 513), (torch.bfloat16, 16 * world * 64)):
         buf, off = heap.alloc((n,), dtype)
-        for it in range(3):
-            g = torch.Generator().manual_seed(it)
+        for it, algo in enumerate(algos):
+            if algo == 1 and n * buf.element_size() > (2 << 20):
+                continue
             vals = [torch.randn(n, generator=torch.Generator().manual_seed(10 * it + r)) for r in range(world)]
             buf.copy_(vals[rank].to(dtype))
-            heap.allreduce_(buf, off, 1.0 / world)
+            heap.allreduce_(buf, off, 1.0 / world, algo=algo)
             want = sum(v.to(dtype).float() for v in vals) / world
             torch.cuda.synchronize()
-            assert torch.allclose(buf.float().cpu(), want, atol=2e-2, rtol=2e-2), (dtype, it)
+            assert torch.allclose(buf.float().cpu(), want, atol=2e-2, rtol=2e-2), (dtype, n, algo)
+        # owner-side reduction (reduce-scatter half), overwriting and accumulating, by peer loads and by the switch
+        vals = [torch.randn(n, generator=torch.Generator().manual_seed(77 + r)) for r in range(world)]
+        buf.copy_(vals[rank].to(dtype))
+        for mc in ([False, True] if heap.has_multicast else [False]):
+            out = torch.ones(n, device=device, dtype=dtype)
+            heap.barrier()
+            heap.comm.reduce_to(off, out, 0.5, 2.0, mc)
+            heap.barrier()
+            torch.cuda.synchronize()
+            want = 2.0 + 0.5 * sum(v.to(dtype).float() for v in vals)
+            assert torch.allclose(out.float().cpu(), want, atol=3e-2, rtol=2e-2), (dtype, n, mc)
     # peer views + barrier: every rank writes its id into the next rank's buffer
     slot, off = heap.alloc((8,), torch.float32)
     heap.barrier()
@@ -80,7 +98,8 @@ def scenario_train(mode, optimizer_name, device):
         from himuon_b200.parallel.fsdp import ShardedEngine
         # "fsdp-peer": no gathered copy; the GEMMs read the weights from the owner rank's shard over NVLink
         engine = ShardedEngine(model, use_banks=True, timeout_s=30.0, peer_weights=(mode == "fsdp-peer"),
-                               weights=opts[0] if opts else None, grads=opts[1] if len(opts) > 1 else "replicated")
+                               weights=opts[0] if opts else None, grads=opts[1] if len(opts) > 1 else "replicated",
+                               nvls="nvls" in opts)
         if mode == "fsdp-peer":
             assert any(st.gathered is None for st in engine.state.values()) or world == 1
         if opts and world > 1:
@@ -95,7 +114,8 @@ def scenario_train(mode, optimizer_name, device):
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
         # 5 layers in buckets of 2: three buckets, the last one short
-        engine = DataParallelEngine(model, timeout_s=30.0, bucket_layers=2, overlap="serial" not in opts)
+        engine = DataParallelEngine(model, timeout_s=30.0, bucket_layers=2, overlap="serial" not in opts,
+                                    nvls="nvls" in opts)
         assert engine.overlap == (world > 1 and "serial" not in opts)
     lr = 1e-3 if optimizer_name == "adamw" else 0.02
     ns = argparse.Namespace(lr=lr, weight_decay=0.1, tile_size=128, cuda_graph=True, cuda_graph_warmup=1)
@@ -177,7 +197,7 @@ if __name__ == "__main__":
     dist.init_process_group("nccl", device_id=device)
     try:
         if scenario == "collectives":
-            scenario_collectives(device)
+            scenario_collectives(device, multicast=(mode == "nvls"))
         elif scenario == "train":
             scenario_train(mode, optname, device)
         else:

@@ -23,6 +23,28 @@ def _run(nproc, *argv, timeout=600):
     return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
 
 
+# The multicast (NVLS) cases bind every rank's memory to one NVLink multicast object.  They run only when asked for
+# (HIMUON_TEST_NVLS=1): a rank that dies while bound can disturb the other GPUs of a shared machine, so the default
+# multi-GPU tier, and every failure-detection case, stays on plain peer loads and stores.
+nvls_opt_in = pytest.mark.skipif(os.environ.get("HIMUON_TEST_NVLS") != "1", reason="set HIMUON_TEST_NVLS=1 to run the multicast cases")
+
+
+@needs2
+@nvls_opt_in
+def test_multicast_collectives():
+    r = _run(2, "collectives", "nvls", "-")
+    assert "COLLECTIVES OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+@needs2
+@nvls_opt_in
+@pytest.mark.parametrize("mode,opt", [("fsdp:gathered:sharded:nvls", "himuon"), ("fsdp:ring:replicated:nvls", "himuon"),
+                                      ("ddp:overlap:nvls", "adamw")])
+def test_multicast_training_matches_single_process(mode, opt):
+    r = _run(2, "train", mode, opt)
+    assert "PARITY OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
 @needs2
 def test_peer_memory_collectives():
     r = _run(min(N_GPUS, 8), "collectives", "-", "-")
