@@ -63,12 +63,15 @@ class _BankState:
 class ShardedEngine:
     def __init__(self, model: nn.Module, use_banks: bool = True, cpu_offload: bool = False, timeout_s: float = 120.0,
                  gather_blocks: int = 0, peer_weights: bool = False, weights: str | None = None,
-                 grads: str = "replicated", nvls: bool = False):
+                 grads: str = "replicated", nvls: bool = False, debug: bool = False):
         """``weights``: ``"gathered"`` (default), ``"ring"`` or ``"peer"`` (``peer_weights=True`` is the older spelling
         of the last); ``grads``: ``"replicated"`` (default) or ``"sharded"``; see the module docstring.
         ``nvls``: bind the symmetric heap to an NVLink multicast object; the gradient reductions onto the owners then
         read through it (``multimem.ld_reduce``: the switch sums the ranks' copies, the owner receives one copy's worth
         of bytes instead of ``world - 1``) and the replicated parameters' all-reduce goes through the switch too.
+        ``debug``: race / overrun checks for development - guard zones after every heap region (``heap.check_canaries()``,
+        verified in ``zero_grad``), and staging slots and group gradient buffers are filled with NaN whenever their
+        contents become stale, so a kernel that reads a slot before its copy has landed poisons the loss visibly.
         ``cpu_offload``: keep the optimizer's state tensors in pinned host memory between steps (see
         :class:`OptimizerStateOffload`; the reference's ``--cpu-offload``, ``train_fsdp.py:58,120``)."""
         self.model = model
@@ -111,7 +114,10 @@ class ShardedEngine:
             slots = n_local                                            # the owned shard
             slots += n_local * self.world if grads == "replicated" else unit * self.world   # gradient buffer
             need += slots * H * W * esz + 16384
-        self.heap = SymmetricHeap(need, self.device, timeout_s, multicast=nvls)
+        self.debug = bool(debug)
+        if self.debug:
+            need += 64 * SymmetricHeap.CANARY_BYTES + 64 * 1024
+        self.heap = SymmetricHeap(need, self.device, timeout_s, multicast=nvls, canaries=self.debug)
         self.nvls = self.heap.has_multicast
 
         # ---- replicated parameters: gradients in one flat symmetric region per dtype
@@ -350,6 +356,12 @@ class ShardedEngine:
         and every group-staged gradient sink starts by overwriting."""
         self._slot_group = [None, None]
         self._slot_ready = [None, None]
+        if self.debug:
+            for st in self.state.values():
+                for slot in (st.ring or []):
+                    slot.fill_(float("nan"))
+                if st.gring is not None:
+                    st.gring.fill_(float("nan"))
         if self.grads_mode == "sharded":
             for st in self.state.values():
                 for s in st.sinks:
@@ -484,6 +496,10 @@ class ShardedEngine:
                 st.param.grad = None
         self._slot_group = [None, None]            # the shards changed: staged copies are stale
         self._slot_ready = [None, None]
+        if self.debug:
+            bad = self.heap.check_canaries()
+            if bad:
+                raise RuntimeError(f"ShardedEngine(debug): heap guard zones overwritten at offsets {bad}")
 
     def _regather(self):
         if all(st.gathered is None for st in self.state.values()):

@@ -38,8 +38,18 @@ def _world():
 
 
 class SymmetricHeap:
-    def __init__(self, nbytes: int, device: torch.device, timeout_s: float = 120.0, multicast: bool = False):
+    CANARY_BYTES = 1024
+    CANARY_VALUE = 0xA5
+
+    def __init__(self, nbytes: int, device: torch.device, timeout_s: float = 120.0, multicast: bool = False,
+                 canaries: bool = False):
+        """``canaries``: debugging aid against out-of-bounds writes by the kernels that address the heap through raw
+        pointers (there is no memory checker to lean on): every region gets a guard zone filled with a byte pattern
+        after it, and ``check_canaries()`` reports any zone that no longer holds the pattern.  Every rank must pass
+        the same value (the regions' offsets have to agree)."""
         self.rank, self.world = _world()
+        self.canaries = bool(canaries)
+        self._guards: list[int] = []
         self.has_multicast = False
         self._vmm = False
         self.device = torch.device(device)
@@ -163,10 +173,24 @@ class SymmetricHeap:
             numel *= int(s)
         nbytes = numel * torch.empty((), dtype=dtype).element_size()
         offset = -(-self.cursor // _ALIGN) * _ALIGN
-        if offset + nbytes > self.nbytes:
-            raise MemoryError(f"symmetric heap exhausted: need {offset + nbytes} bytes, have {self.nbytes}")
-        self.cursor = offset + nbytes
+        guard = self.CANARY_BYTES if self.canaries else 0
+        if offset + nbytes + guard > self.nbytes:
+            raise MemoryError(f"symmetric heap exhausted: need {offset + nbytes + guard} bytes, have {self.nbytes}")
+        self.cursor = offset + nbytes + guard
+        if guard:
+            self.view(self.rank, offset + nbytes, (guard,), torch.uint8).fill_(self.CANARY_VALUE)
+            self._guards.append(offset + nbytes)
         return self.view(self.rank, offset, shape, dtype), offset
+
+    def check_canaries(self) -> list[int]:
+        """Offsets of the guard zones on this rank that were overwritten (empty when all are intact or canaries are
+        off).  Synchronises with the device."""
+        bad = []
+        for off in self._guards:
+            zone = self.view(self.rank, off, (self.CANARY_BYTES,), torch.uint8)
+            if not bool((zone == self.CANARY_VALUE).all()):
+                bad.append(off)
+        return bad
 
     def view(self, rank: int, offset: int, shape, dtype) -> torch.Tensor:
         """Rank ``rank``'s copy of the region at ``offset`` as a tensor on this device."""

@@ -43,7 +43,7 @@ def scenario_train(mode, optimizer_name):
     if mode == "fsdp":
         from himuon_b200.parallel.fsdp import ShardedEngine
         engine = ShardedEngine(model, use_banks=True, weights=opts[0] if opts else None,
-                               grads=opts[1] if len(opts) > 1 else "replicated")
+                               grads=opts[1] if len(opts) > 1 else "replicated", debug="debug" in opts)
         if opts and world > 1:
             assert engine.weights_mode == opts[0] and engine.grads_mode == opts[1] and engine.uses_fences
             b = engine.bank_bytes()

@@ -99,7 +99,7 @@ def scenario_train(mode, optimizer_name, device):
         # "fsdp-peer": no gathered copy; the GEMMs read the weights from the owner rank's shard over NVLink
         engine = ShardedEngine(model, use_banks=True, timeout_s=30.0, peer_weights=(mode == "fsdp-peer"),
                                weights=opts[0] if opts else None, grads=opts[1] if len(opts) > 1 else "replicated",
-                               nvls="nvls" in opts)
+                               nvls="nvls" in opts, debug="debug" in opts)
         if mode == "fsdp-peer":
             assert any(st.gathered is None for st in engine.state.values()) or world == 1
         if opts and world > 1:

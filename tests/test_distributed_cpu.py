@@ -23,7 +23,7 @@ def _run(nproc, *argv, timeout=300):
 @pytest.mark.parametrize("mode,opt,nproc", [("fsdp", "himuon", 2), ("fsdp", "muon-fsdp", 2), ("ddp", "himuon", 2),
                                             ("fsdp", "himuon", 4), ("fsdp", "adamw", 2),
                                             ("fsdp:ring:replicated", "himuon", 2), ("fsdp:gathered:sharded", "himuon", 2),
-                                            ("fsdp:ring:sharded:ckpt", "himuon", 2), ("fsdp:ring:sharded", "adamw", 2),
+                                            ("fsdp:ring:sharded:ckpt:debug", "himuon", 2), ("fsdp:ring:sharded", "adamw", 2),
                                             ("fsdp:ring:sharded", "muon-fsdp", 3), ("ddp:overlap", "adamw", 2)])
 def test_multi_rank_training_matches_single_process(mode, opt, nproc):
     r = _run(nproc, "train", mode, opt)

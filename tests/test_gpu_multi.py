@@ -55,7 +55,7 @@ def test_peer_memory_collectives():
 @pytest.mark.parametrize("mode,opt", [("fsdp", "himuon"), ("ddp", "himuon"), ("fsdp", "muon-fsdp"), ("fsdp", "adamw"),
                                       ("fsdp-peer", "himuon"), ("fsdp:ring:replicated", "himuon"),
                                       ("fsdp:ring:replicated:graph", "himuon"), ("fsdp:gathered:sharded", "himuon"),
-                                      ("fsdp:ring:sharded:graph:ckpt", "himuon"), ("fsdp:ring:sharded", "adamw"),
+                                      ("fsdp:ring:sharded:graph:ckpt:debug", "himuon"), ("fsdp:ring:sharded", "adamw"),
                                       ("fsdp:ring:sharded", "muon-fsdp"), ("ddp:overlap:graph", "himuon"),
                                       ("ddp:serial", "adamw")])
 def test_multi_gpu_training_matches_single_process(mode, opt):

@@ -91,3 +91,23 @@ def test_time_budget_and_seed():
 def test_metric_line_format():
     line = format_metrics({"step": 3, "lr": 0.0125, "loss": 2.34567, "tokens": 1234567, "eval_loss": 1.5})
     assert line == "Step: 3 LR: 0.012500 Training loss: 2.3457, Tokens: 1,234,567, Eval loss: 1.5000"
+
+
+def test_symmetric_heap_guard_zones_catch_an_overrun():
+    import torch
+
+    from himuon_b200.parallel.symm import SymmetricHeap
+
+    heap = SymmetricHeap(1 << 16, torch.device("cpu"), canaries=True)
+    a, off_a = heap.alloc((100,), torch.float32)
+    b, off_b = heap.alloc((64,), torch.bfloat16)
+    assert off_b >= off_a + 400 + SymmetricHeap.CANARY_BYTES
+    a.fill_(1.0)
+    b.fill_(2.0)
+    assert heap.check_canaries() == []
+    # a write that runs past the end of the first region lands in its guard zone
+    heap.view(0, off_a, (104,), torch.float32)[100:].fill_(3.0)
+    assert heap.check_canaries() == [off_a + 400]
+    plain = SymmetricHeap(1 << 12, torch.device("cpu"))
+    plain.alloc((8,), torch.float32)
+    assert plain.check_canaries() == []
