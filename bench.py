@@ -205,6 +205,15 @@ def run_ours(args):
         e2e = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": trainer.h2d_bytes // args.steps, "d2h_bytes_per_step": trainer.d2h_bytes // args.steps,
                "ms_per_step": ms_e2e / args.steps, "last_loss": losses[-1]}
+    # Where a step goes: device time per phase (CUDA events, max over ranks) over two more steps, outside the timed
+    # regions.  grad_reduce + regather_reset is the communication that is not hidden behind compute.
+    from himuon_b200.utils import PhaseTimer
+    trainer.phases = PhaseTimer(True, device)
+    n_phase = 2
+    for i in range(n_phase):
+        trainer.train_step(dev_batches[args.warmup + (i % args.steps)])
+    phases = {k: round(v / n_phase, 3) for k, v in trainer.phases.summary().items()}
+    trainer.phases = PhaseTimer(False)
     ops.check_status()
     if rank == 0:
         out = {
@@ -219,7 +228,8 @@ def run_ours(args):
                        "forward_backward": "eager" if args.no_step_graph else "micro-batch CUDA graphs (public Trainer option)",
                        "activation_checkpointing": checkpointing,
                        "l2": "no flush: each step streams >8 GB of weights and activations (L2 is 126 MB)"},
-            "optimizer_step_ms": opt_ms,
+            "optimizer_step_ms": opt_ms, "phases_ms_per_step": phases,
+            "exposed_comm_ms_per_step": round(phases.get("grad_reduce", 0.0) + phases.get("regather_reset", 0.0), 3),
             "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": launches, "impl": "ours",
         }
         print(json.dumps(out), flush=True)

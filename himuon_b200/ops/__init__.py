@@ -40,6 +40,18 @@ def use_kernels(t: torch.Tensor) -> bool:
     return t.is_cuda and t.dtype == torch.bfloat16
 
 
+_WARNED: set = set()
+
+
+def _warn_torch_path(op: str, why: str) -> None:
+    """Says once per (op, reason) that a bf16 CUDA tensor is taking the plain PyTorch implementation of an op."""
+    if (op, why) not in _WARNED:
+        _WARNED.add((op, why))
+        import warnings
+        warnings.warn(f"himuon_b200.ops.{op}: {why}; running the PyTorch implementation instead of the sm_100a kernel",
+                      stacklevel=3)
+
+
 def check_status() -> None:
     """Raise if any kernel's bounded wait ran out since the last check (synchronises)."""
     code = _ext.ext().status(True)
@@ -426,6 +438,8 @@ def head_norm_rope(x2d, w, cos_sin, heads: int, seq_len: int, head_dim: int, eps
     backward pass may overwrite the gradient it receives with the gradient it returns."""
     if use_kernels(x2d) and head_dim == 128:
         return _HeadNormRopeFn.apply(x2d, w, cos_sin, heads, seq_len, eps, _deferrable(w, defer_dw), inplace_grad)
+    if use_kernels(x2d):
+        _warn_torch_path("head_norm_rope", f"head_dim {head_dim} (the kernel is written for 128)")
     T = x2d.shape[0]
     x = x2d.reshape(T // seq_len, seq_len, heads, head_dim)
     if w is not None:
@@ -507,6 +521,21 @@ def attention(q2d, k2d, v2d, B: int, S: int, Hq: int, Hkv: int, head_dim: int, s
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     if use_kernels(q2d) and head_dim == 128:
         return _FlashAttnFn.apply(q2d, k2d, v2d, B, S, Hq, Hkv, scale)
+    if use_kernels(q2d) and head_dim < 128 and head_dim % 8 == 0:
+        # Smaller heads (64 in Llama-3.2-1B and llama_220m) run the same tcgen05 kernels zero-padded to 128: zeros in
+        # q and k add nothing to the scores, zeros in v give zero output columns, which are cut off again.  Twice the
+        # tensor work of a native 64-wide kernel, but no S x S score matrix in memory; autograd differentiates the
+        # padding and the slice.
+        T = q2d.shape[0]
+        pad = 128 - head_dim
+
+        def widen(x, heads):
+            return torch.nn.functional.pad(x.reshape(T, heads, head_dim), (0, pad)).reshape(T, heads * 128)
+
+        o = _FlashAttnFn.apply(widen(q2d, Hq), widen(k2d, Hkv), widen(v2d, Hkv), B, S, Hq, Hkv, scale)
+        return o.reshape(T, Hq, 128)[:, :, :head_dim].reshape(T, Hq * head_dim)
+    if use_kernels(q2d):
+        _warn_torch_path("attention", f"head_dim {head_dim} (the kernels take 128, or a multiple of 8 below it)")
     q = q2d.reshape(B, S, Hq, head_dim)
     k = k2d.reshape(B, S, Hkv, head_dim)
     v = v2d.reshape(B, S, Hkv, head_dim)

@@ -245,3 +245,40 @@ def test_cpu_offload_keeps_optimizer_state_on_the_host_between_steps(opt_name):
     for n in p0:
         c = _cos(p0[n], p1[n]).item()
         assert c > 0.9999, (n, c)
+
+
+def test_head_dim_64_models_run_attention_on_the_kernels():
+    """Llama-3.2-1B / llama_220m have 64-wide heads: attention runs zero-padded on the 128-wide tcgen05 kernels (no
+    S x S score matrix), the per-head norm / RoPE kernel is replaced by the PyTorch ops with a warning, and loss and
+    gradients follow the fp32 model."""
+    import warnings
+
+    from himuon_b200 import ops
+    from himuon_b200.models import CausalLM, DecoderConfig
+
+    cfg = DecoderConfig(model_type="llama", vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6, rope_theta=10000.0,
+                        tie_word_embeddings=False, max_position_embeddings=512)
+    torch.manual_seed(0)
+    ref_model = CausalLM(cfg).cuda().float()
+    ker_model = copy.deepcopy(ref_model).bfloat16()
+    with torch.no_grad():
+        for pr, pk in zip(ref_model.parameters(), ker_model.parameters()):
+            pr.copy_(pk.float())
+    ids = torch.randint(0, 2048, (2, 256), device="cuda")
+    ops._WARNED.clear()
+    with warnings.catch_warnings(record=True) as caught:
+        warnings.simplefilter("always")
+        peak0 = torch.cuda.max_memory_allocated()
+        out_k = ker_model(ids, labels=ids)
+        out_k.loss.backward()
+    assert any("head_norm_rope" in str(w.message) for w in caught)
+    assert not any("ops.attention" in str(w.message) for w in caught), "attention left the kernel path"
+    out_r = ref_model(ids, labels=ids)
+    out_r.loss.backward()
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert abs(out_k.loss.item() - out_r.loss.item()) < 3e-2
+    for (n, pr), pk in zip(ref_model.named_parameters(), ker_model.parameters()):
+        c = _cos(pr.grad, pk.grad).item()
+        assert c > 0.98, (n, c)
