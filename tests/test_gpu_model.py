@@ -46,10 +46,16 @@ def test_model_loss_and_grads_match_reference(model_type):
     ops.check_status()
     assert abs(out_k.loss.item() - out_r.loss.item()) < 3e-2, (out_k.loss.item(), out_r.loss.item())
     names = [n for n, _ in ref_model.named_parameters()]
+    worst = []
     for n, pr, pk in zip(names, ref_model.parameters(), ker_model.parameters()):
         assert pk.grad is not None, n
         c = _cos(pr.grad, pk.grad).item()
-        assert c > 0.98, f"gradient of {n} diverges from the reference (cosine {c:.4f})"
+        rel = abs(pk.grad.float().norm().item() / (pr.grad.norm().item() + 1e-12) - 1.0)
+        worst.append((c, rel, n))
+        # direction and size of every parameter's gradient: a bf16 forward/backward against the fp32 model
+        assert c > 0.99, f"gradient of {n} diverges from the reference (cosine {c:.4f})"
+        assert rel < 0.05, f"gradient norm of {n} is off by {rel:.3%}"
+    print("lowest cosine", min(worst)[:3:2], "largest norm error", max(worst, key=lambda t: t[1])[1:])
 
 
 def test_train_steps_himuon_graph_matches_eager():
