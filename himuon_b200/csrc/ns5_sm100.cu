@@ -2,8 +2,13 @@
 //
 // One CTA owns one tile for the whole computation: X, A = X X^T and B = c*A*A + b*A live in
 // swizzled shared memory as bf16 UMMA operands, every product runs on tcgen05 with fp32
-// accumulators in TMEM (256 columns, reused between the three products of an iteration), and
-// nothing but the input and the result touches HBM.  Rounding points follow the reference's
+// accumulators in TMEM, and nothing but the input and the result touches HBM.  The three products
+// of an iteration form a chain (each is drained to shared memory before the next is issued), so
+// the chain's latency is hidden by co-resident CTAs, and the kernel keeps its footprint small to
+// fit as many as possible: B overwrites A in place (every thread rewrites the row chunks it has
+// just read), and tiles up to 128 columns wide use a single 128-column accumulator for all three
+// products - 64 KB of shared memory and 128 TMEM columns per CTA, three CTAs per SM.  Wider tiles
+// need 256 columns for B*X and run two CTAs per SM.  Rounding points follow the reference's
 // fused Triton kernel (src/himuon/triton_kernels/ns5_smem.py:46-104): normalise in fp32 then
 // round; A, B and B*X are rounded to bf16; X <- bf16(bf16(B X) + a*X).
 //
@@ -39,13 +44,15 @@ __global__ void __launch_bounds__(128)
 ns5_fused_kernel(const __grid_constant__ CUtensorMap tmX, __nv_bfloat16* __restrict__ out, long long n_tiles, int m,
                  int steps, float eps, int* status) {
   constexpr int N = NCH * 64;
+  constexpr int TM_COLS = N <= 128 ? 128 : 256;            // TMEM columns of this CTA
+  constexpr uint32_t A2_COL = TM_COLS == 256 ? 128 : 0;    // A*A lands beside A when there is room, else over it
   constexpr float ca = 3.4445f, cb = -4.7750f, cc = 2.0315f;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align_up_1024(smem_raw);
   uint8_t* sX = smem;
   uint8_t* sA = smem + NCH * NS_HALF;
-  uint8_t* sB = sA + 2 * NS_HALF;
-  NsBars* bars = reinterpret_cast<NsBars*>(sB + 2 * NS_HALF);
+  uint8_t* sB = sA;                                        // B replaces A in place
+  NsBars* bars = reinterpret_cast<NsBars*>(sA + 2 * NS_HALF);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -58,7 +65,7 @@ ns5_fused_kernel(const __grid_constant__ CUtensorMap tmX, __nv_bfloat16* __restr
     bars->abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 0) tmem_alloc(&bars->tmem_slot, 256);
+  if (warp == 0) tmem_alloc(&bars->tmem_slot, TM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -134,11 +141,12 @@ ns5_fused_kernel(const __grid_constant__ CUtensorMap tmX, __nv_bfloat16* __restr
       tc_fence_before();
       __syncthreads();
 
-      // ---- A2 = A A (A symmetric, so A doubles as the K-major B operand) -> TMEM columns [128,256)
+      // ---- A2 = A A (A symmetric, so A doubles as the K-major B operand).  A's accumulator has been drained to
+      // shared memory by every thread (the barrier above), so A2 may take its place.
       if (threadIdx.x == 0) {
         tc_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) umma_ss(tmem + 128, ns_desc_k(a_base, ks), ns_desc_k(a_base, ks), idesc_aat, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) umma_ss(tmem + A2_COL, ns_desc_k(a_base, ks), ns_desc_k(a_base, ks), idesc_aat, ks > 0 ? 1u : 0u);
         umma_commit(&bars->mma);
       }
       if (!mbar_wait(&bars->mma, mma_phase, abort_flag, status, 5)) { ok = false; break; }
@@ -147,7 +155,7 @@ ns5_fused_kernel(const __grid_constant__ CUtensorMap tmX, __nv_bfloat16* __restr
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32], a4[16];
-        tmem_ld32(tmem + 128 + lane_off + c * 32, v);
+        tmem_ld32(tmem + A2_COL + lane_off + c * 32, v);
         tmem_ld_wait();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -215,7 +223,7 @@ ns5_fused_kernel(const __grid_constant__ CUtensorMap tmX, __nv_bfloat16* __restr
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    tmem_dealloc(tmem, 256);
+    tmem_dealloc(tmem, TM_COLS);
   }
 }
 
@@ -224,7 +232,8 @@ bool ns5_fused_supported(int m, int n) { return m >= 1 && m <= 128 && m <= n && 
 template <int NCH>
 static void launch_ns5(const void* x_in, void* x_out, long long n_tiles, int m, int steps, float eps, cudaStream_t s) {
   constexpr int N = NCH * 64;
-  constexpr size_t SMEM = 1024 + (NCH + 4) * NS_HALF + 256;
+  constexpr size_t SMEM = 1024 + (NCH + 2) * NS_HALF + 256;
+  constexpr int TM_COLS = N <= 128 ? 128 : 256;
   auto kern = ns5_fused_kernel<NCH>;
   static bool attr = false;
   if (!attr) { cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM); attr = true; }
@@ -232,7 +241,9 @@ static void launch_ns5(const void* x_in, void* x_out, long long n_tiles, int m, 
   const uint64_t strides[2] = {static_cast<uint64_t>(N) * 2, static_cast<uint64_t>(N) * 2 * m};
   const uint32_t box[3] = {64, 128, 1};
   const CUtensorMap tm = make_tmap(x_in, 3, dims, strides, box, 2, true);
-  const int per_sm = SMEM <= 110 * 1024 ? 2 : 1;
+  // resident CTAs per SM: bounded by shared memory (227 KB, plus 1 KB the driver keeps per CTA) and by TMEM (512 columns)
+  const int by_smem = static_cast<int>((227 * 1024) / (SMEM + 1024)), by_tmem = 512 / TM_COLS;
+  const int per_sm = by_smem < by_tmem ? by_smem : by_tmem;
   const long long cap = static_cast<long long>(num_sms()) * per_sm;
   const int grid = static_cast<int>(n_tiles < cap ? n_tiles : cap);
   kern<<<grid, 128, SMEM, s>>>(tm, reinterpret_cast<__nv_bfloat16*>(x_out), n_tiles, m, steps, eps, status_word_ptr());

@@ -352,17 +352,13 @@ class ShardedEngine:
         return h, delta
 
     def _begin_pass(self):
-        """A new forward pass: nothing is assumed about what the staging slots hold (the optimizer may have stepped),
-        and every group-staged gradient sink starts by overwriting."""
-        self._slot_group = [None, None]
-        self._slot_ready = [None, None]
-        if self.debug:
-            for st in self.state.values():
-                for slot in (st.ring or []):
-                    slot.fill_(float("nan"))
-                if st.gring is not None:
-                    st.gring.fill_(float("nan"))
+        """A new forward pass.  Group-staged gradient sinks start by overwriting.  The weight staging slots keep what
+        they hold: the weights only change in the optimizer step (``zero_grad`` invalidates the slots), and a backward
+        pass ends with groups 0 and 1 staged, which is exactly what the next micro-batch's forward pass needs first."""
         if self.grads_mode == "sharded":
+            if self.debug:
+                for st in self.state.values():
+                    st.gring.fill_(float("nan"))
             for st in self.state.values():
                 for s in st.sinks:
                     s.reset()
@@ -497,6 +493,9 @@ class ShardedEngine:
         self._slot_group = [None, None]            # the shards changed: staged copies are stale
         self._slot_ready = [None, None]
         if self.debug:
+            for st in self.state.values():
+                for slot in (st.ring or []):
+                    slot.fill_(float("nan"))
             bad = self.heap.check_canaries()
             if bad:
                 raise RuntimeError(f"ShardedEngine(debug): heap guard zones overwritten at offsets {bad}")
