@@ -3,8 +3,11 @@
 Semantics of ``src/himuon/optimizers/muon.py:13-195``: momentum (+Nesterov), five quintic NS
 iterations on the whole matrix, Moonlight step scale ``0.2*sqrt(max(A, B))``; parameters with
 ``use_muon=False`` take Adam with ``u = m/(eps + sqrt(v))`` and step ``lr / (bc1/sqrt(bc2))``.
-On CUDA, NS runs on the tcgen05 kernels (same-shape matrices are batched into one call) and the
-fallback is one multi-tensor launch.
+On CUDA the whole muon part of a step runs on the library's kernels: momentum + Nesterov, whole-matrix
+Newton-Schulz (same-shape matrices batched) and the scaled, weight-decayed update are exactly HiMuon's step with a
+tile that covers every matrix, so ``Muon`` drives a private :class:`HiMuon` over its muon groups (sharing the
+per-parameter state dicts, so ``state_dict()`` still shows ``momentum_buffer``); the AdamW fallback is one multi-tensor
+launch in Muon's own convention.  DTensor parameters and CPU tensors take the PyTorch ops.
 """
 
 from __future__ import annotations
@@ -31,6 +34,39 @@ class Muon(Optimizer):
         super().__init__(params, defaults)
         self._table = AdamTable()
         self._ws = ns_ops.NSWorkspace()
+        self._kernel_muon = None        # private HiMuon over the muon groups (CUDA only), built on first use
+
+    def _muon_on_kernels(self) -> bool:
+        """True when every muon parameter with a gradient is a plain 2-D / 3-D bf16 or fp32 CUDA tensor."""
+        seen = False
+        for g in self.param_groups:
+            if not g["use_muon"]:
+                continue
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                if hasattr(p, "to_local") or not p.is_cuda or p.ndim not in (2, 3) \
+                        or p.dtype not in (torch.bfloat16, torch.float32) or p.grad.dtype != p.dtype:
+                    return False
+                seen = True
+        return seen
+
+    def _step_muon_kernels(self):
+        from .himuon import HiMuon
+        muon_groups = [g for g in self.param_groups if g["use_muon"]]
+        keys = ("lr", "weight_decay", "momentum", "nesterov", "ns_steps")
+        if self._kernel_muon is None or [id(p) for g in muon_groups for p in g["params"]] != self._kernel_muon_ids:
+            inner = HiMuon([{"params": g["params"], **{k: g[k] for k in keys}} for g in muon_groups],
+                           tile_size=10 ** 9, lr_adjust="tile", cuda_graph=False)
+            for g in muon_groups:                         # the same per-parameter dicts: momentum buffers appear in ours
+                for q in g["params"]:
+                    inner.state[q] = self.state[q]
+            self._kernel_muon = inner
+            self._kernel_muon_ids = [id(p) for g in muon_groups for p in g["params"]]
+        for src, dst in zip(muon_groups, self._kernel_muon.param_groups):
+            for k in keys:
+                dst[k] = src[k]
+        self._kernel_muon.step()
 
     @staticmethod
     def adjust_lr_for_muon(lr, shape):
@@ -48,6 +84,7 @@ class Muon(Optimizer):
         """Restores the state and drops the device entry table (it holds the addresses of the replaced moments)."""
         super().load_state_dict(state_dict)
         self._table = AdamTable()
+        self._kernel_muon = None
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -55,6 +92,10 @@ class Muon(Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        if self._muon_on_kernels():
+            self._step_muon_kernels()
+            self._step_adamw()
+            return loss
         for group in self.param_groups:
             if not group["use_muon"]:
                 continue
