@@ -51,6 +51,28 @@ def case_ns512():
     print(f"NS5 512 tiles of 512x512: {ms:.3f} ms, {512 * 15 * 2 * 512 ** 3 / 1e9 / ms:.0f} TFLOP/s")
 
 
+def case_ns1024():
+    x = torch.randn(96, 1024, 1024, device="cuda", dtype=torch.bfloat16)
+    ws = ns_ops.NSWorkspace()
+    ms = _time(lambda: ns_ops.ns_inplace_cuda(x.clone(), 5, workspace=ws), n=3)
+    print(f"NS5 96 tiles of 1024x1024: {ms:.3f} ms, {96 * 15 * 2 * 1024 ** 3 / 1e9 / ms:.0f} TFLOP/s (full-product FLOPs)")
+
+
+def case_ns_products():
+    """The three products of one Newton-Schulz iteration on 512 tiles of 512x512, one launch each: the two symmetric
+    ones with and without the symmetric-output mode."""
+    from himuon_b200 import ops
+    X = torch.randn(512, 512, 512, device="cuda", dtype=torch.bfloat16) / 23
+    A, Bm, Y = torch.empty_like(X), torch.empty_like(X), torch.empty_like(X)
+    fl = 512 * 2 * 512 ** 3 / 1e9
+    for sym in (False, True):
+        m1 = _time(lambda: ops.gemm(X, X, trans_b=True, out=A, symmetric=sym))
+        m2 = _time(lambda: ops.gemm(A, A, trans_b=True, alpha=2.0315, beta=-4.775, aux=A, out=Bm, symmetric=sym))
+        print(f"symmetric={sym}: X X^T {m1:.3f} ms ({fl / m1:.0f} TFLOP/s of full-product FLOPs) | c A A + b A {m2:.3f} ms ({fl / m2:.0f})")
+    m3 = _time(lambda: ops.gemm(Bm, X, alpha=1.0, beta=3.4445, aux=X, out=Y, round_acc=True))
+    print(f"B X + a X {m3:.3f} ms ({fl / m3:.0f} TFLOP/s)")
+
+
 def case_ns128():
     x = torch.randn(8192, 128, 128, device="cuda", dtype=torch.bfloat16)
     y = torch.empty_like(x)
@@ -70,6 +92,22 @@ def case_attn():
     do, dq, dk, dv, delta = torch.randn_like(q), torch.empty_like(q), torch.empty_like(k), torch.empty_like(k), torch.empty_like(lse)
     part = torch.empty(2, B * S, Hq * 128, device="cuda", dtype=torch.bfloat16)
     msb = _time(lambda: ext().flash_attn_bwd(do, q, k, v, o, lse, dq, dk, dv, delta, part, B, S, Hq, Hkv, sc))
+    print(f"attention B{B} S{S} H{Hq}/{Hkv}: fwd {ms:.3f} ms {fl / ms:.0f} TFLOP/s, bwd {msb:.3f} ms {2.5 * fl / msb:.0f} TFLOP/s")
+
+
+def case_attn_train():
+    """The attention shape of the headline training step: micro-batch 2 x sequence 1024, 32 query / 8 KV heads."""
+    B, S, Hq, Hkv = 2, 1024, 32, 8
+    q = torch.randn(B * S, Hq * 128, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(B * S, Hkv * 128, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn_like(k)
+    o, lse = torch.empty_like(q), torch.empty(B * Hq * S, device="cuda")
+    sc = 1 / math.sqrt(128)
+    fl = 4 * B * Hq * S * S * 128 / 2 / 1e9
+    ms = _time(lambda: ext().flash_attn_fwd(q, k, v, o, lse, B, S, Hq, Hkv, sc), n=20)
+    do, dq, dk, dv, delta = torch.randn_like(q), torch.empty_like(q), torch.empty_like(k), torch.empty_like(k), torch.empty_like(lse)
+    part = torch.empty(2, B * S, Hq * 128, device="cuda", dtype=torch.bfloat16)
+    msb = _time(lambda: ext().flash_attn_bwd(do, q, k, v, o, lse, dq, dk, dv, delta, part, B, S, Hq, Hkv, sc), n=20)
     print(f"attention B{B} S{S} H{Hq}/{Hkv}: fwd {ms:.3f} ms {fl / ms:.0f} TFLOP/s, bwd {msb:.3f} ms {2.5 * fl / msb:.0f} TFLOP/s")
 
 
@@ -121,7 +159,8 @@ def case_step():
     print(f"step case done, loss {loss.item():.3f}")
 
 
-CASES = {"gemm": case_gemm, "gemm_wgrad": case_gemm_wgrad, "ns512": case_ns512, "ns128": case_ns128, "attn": case_attn,
+CASES = {"gemm": case_gemm, "gemm_wgrad": case_gemm_wgrad, "ns512": case_ns512, "ns1024": case_ns1024,
+         "ns_products": case_ns_products, "ns128": case_ns128, "attn": case_attn, "attn_train": case_attn_train,
          "optim": case_optim, "step": case_step}
 
 if __name__ == "__main__":
