@@ -12,8 +12,8 @@ the layer axis in whole matrices, so the optimizer needs no collective (the refe
 * **Weights: gathered copy or staging ring** (``weights=``).
 
   - ``"gathered"``: every rank keeps a full bf16 working copy of every bank, refreshed after each optimizer step by
-    one ``multi_copy`` launch that pulls the peers' shards over NVLink; accumulation micro-steps do no parameter
-    communication (180 GB of HBM hold the copy).
+    copy-engine pulls of the peers' shards over NVLink (``gather_blocks > 0`` selects the ``multi_copy`` kernel on that
+    many blocks instead); accumulation micro-steps do no parameter communication (180 GB of HBM hold the copy).
   - ``"ring"``: no full copy.  Layers are taken in groups of ``world`` consecutive layers (one per owner); two
     group-sized staging slots rotate.  While group ``g`` computes, a side stream copies group ``g+1`` (``g-1`` in
     backward) from the owners' shards with the copy engines - no SM is taken from the GEMMs, and rank ``r`` visits
@@ -507,7 +507,20 @@ class ShardedEngine:
             for st in self.state.values():
                 dist.all_gather_into_tensor(st.gathered, st.shard.contiguous())
             return
-        if self._copy_table is None:
+        if self.gather_blocks <= 0:
+            # Copy engines (measured 0.94 of the peer-copy rate against 0.55 for the SM copy kernel at two ranks):
+            # one copy per (owner, bank), owners in the order rank+1, rank+2, ... so that every owner serves one
+            # reader at a time.  The own shard is a local copy.
+            for j in range(self.world):
+                r = (self.rank + j) % self.world
+                for st in self.state.values():
+                    if st.gathered is None:
+                        continue
+                    H, W = st.spec.matrix_shape
+                    src = st.shard if r == self.rank else self.heap.view(r, st.shard_off, (st.n_local, H, W), self.dtype)
+                    st.gathered[r * st.n_local:(r + 1) * st.n_local].copy_(src, non_blocking=True)
+            return
+        if self._copy_table is None:                 # gather_blocks > 0: the multi_copy kernel on that many blocks
             ext = self.heap._ext
             tab, units, n = bytearray(), 0, 0
             for st in self.state.values():

@@ -272,45 +272,48 @@ def test_soap_kernels_match_fp32_torch():
 
 
 def test_soap_kernel_path_follows_the_torch_path():
-    """A SOAP run whose rotations, Gram statistics and update go through the GEMM and the soap_* kernels against the
-    same optimizer forced onto its PyTorch ops, on the same bf16 CUDA tensors.  The gradients have a well separated
-    spectrum: with near-degenerate Gram eigenvalues the eigenbases themselves are ill-conditioned and any two
-    implementations drift apart."""
+    """One SOAP step through the GEMM and the soap_* kernels against the same step through the optimizer's PyTorch
+    ops, from identical state (bases, Gram statistics, moments) and with the same gradient, for three consecutive
+    steps, one of which refreshes the eigenbases.  Longer independent runs are no oracle for this optimizer: the Adam
+    ratio in the eigenbasis blows rounding differences up wherever the gradient has little signal, and the
+    eigenbases of near-degenerate Gram matrices are ill-conditioned, so two correct implementations drift apart."""
+    import copy
+
     from himuon_b200 import ops
     from himuon_b200.optimizers import SOAP
 
     shapes = [(256, 384), (128, 128), (320, 136)]
-    gen = torch.Generator().manual_seed(7)
-    bases = []
-    for (h, w) in shapes:
-        k = min(h, w)
-        L, _ = torch.linalg.qr(torch.randn(h, k, generator=gen))
-        R, _ = torch.linalg.qr(torch.randn(w, k, generator=gen))
-        bases.append((L, torch.logspace(0, -2, k), R))
-
-    def run(use_kernels):
-        torch.manual_seed(0)
-        model = make_linear_model(shapes, dtype=torch.bfloat16, device="cuda")
-        opt = SOAP(model.parameters(), lr=3e-3, precondition_frequency=3, weight_decay=0.01)
-        if not use_kernels:
-            opt._kernel_ok = lambda *a, **k: False
-        start = [p.detach().float().clone() for p in model.parameters()]
-        g = torch.Generator().manual_seed(11)
-        for s in range(7):
-            for p, (L, sv, R) in zip(model.parameters(), bases):
-                coef = sv * (1.0 + 0.3 * torch.randn(sv.shape, generator=g))
-                p.grad = ((L * coef) @ R.t() + 1e-3 * torch.randn(p.shape, generator=g)).bfloat16().cuda()
-            opt.step()
+    kw = dict(lr=3e-3, precondition_frequency=3, weight_decay=0.01)
+    torch.manual_seed(0)
+    model = make_linear_model(shapes, dtype=torch.bfloat16, device="cuda")
+    opt = SOAP(model.parameters(), **kw)
+    opt._kernel_ok = lambda *a, **k: False                      # PyTorch ops only
+    g = torch.Generator().manual_seed(11)
+    for _ in range(5):
+        for p in model.parameters():
+            p.grad = torch.randn(p.shape, generator=g).bfloat16().cuda()
+        opt.step()
+    for nxt in range(3):
+        twin = copy.deepcopy(model)
+        opt_k = SOAP(twin.parameters(), **kw)
+        for p, q in zip(model.parameters(), twin.parameters()):  # same state, dtype for dtype (no load_state_dict cast)
+            opt_k.state[q] = copy.deepcopy(opt.state[p])
+        grads = [torch.randn(p.shape, generator=g).bfloat16().cuda() for p in model.parameters()]
+        before = [p.detach().float().clone() for p in model.parameters()]
+        for p, q, gr in zip(model.parameters(), twin.parameters(), grads):
+            p.grad, q.grad = gr.clone(), gr.clone()
+        n0 = ops.launch_count()
+        opt_k.step()
+        assert ops.launch_count() - n0 >= 10 * len(shapes), "the kernel path did not run"
+        opt.step()
         torch.cuda.synchronize()
-        return [p.detach().float() - s0 for p, s0 in zip(model.parameters(), start)]
-
-    before = ops.launch_count()
-    ker = run(True)
-    assert ops.launch_count() - before > 6 * 8 * len(shapes), "the kernel path did not run"
-    ref = run(False)
+        for p, q, b in zip(model.parameters(), twin.parameters(), before):
+            d_ref, d_ker = p.detach().float() - b, q.detach().float() - b
+            assert torch.isfinite(d_ker).all()
+            c = _cosine(d_ker, d_ref)
+            assert c > 0.995, (nxt, tuple(p.shape), c)
+            assert abs(float(d_ker.norm() / d_ref.norm()) - 1.0) < 0.02, (nxt, tuple(p.shape))
+            gg_r, gg_k = opt.state[p]["GG"], opt_k.state[q]["GG"]
+            for a, bb in zip(gg_r, gg_k):                        # Gram EMA in the GEMM epilogue vs lerp_
+                assert float((a - bb).norm() / a.norm()) < 1e-3
     ops.check_status()
-    for (h, w), dk, dr in zip(shapes, ker, ref):
-        assert torch.isfinite(dk).all()
-        c = _cosine(dk, dr)
-        assert c > 0.97, ((h, w), c)
-        assert abs(float(dk.norm() / dr.norm()) - 1.0) < 0.1, ((h, w), float(dk.norm()), float(dr.norm()))

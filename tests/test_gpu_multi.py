@@ -57,7 +57,8 @@ def test_peer_memory_collectives():
                                       ("fsdp:ring:replicated:graph", "himuon"), ("fsdp:gathered:sharded", "himuon"),
                                       ("fsdp:ring:sharded:graph:ckpt:debug", "himuon"), ("fsdp:ring:sharded", "adamw"),
                                       ("fsdp:ring:sharded", "muon-fsdp"), ("ddp:overlap:graph", "himuon"),
-                                      ("ddp:serial", "adamw")])
+                                      ("ddp:serial", "adamw"), ("fsdp:ring:replicated:fp32ref", "adamw"),
+                                      ("ddp:overlap:fp32ref", "himuon")])
 def test_multi_gpu_training_matches_single_process(mode, opt):
     r = _run(2, "train", mode, opt)
     assert "PARITY OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
