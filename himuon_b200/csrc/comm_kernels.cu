@@ -20,8 +20,8 @@
 
 namespace himuon {
 
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(int* p, int v) {
+  asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
@@ -53,11 +53,13 @@ __device__ __forceinline__ bool wait_flag_ge(const int* flag, int target, unsign
 __device__ __forceinline__ bool block_handshake(CommPeers peers, int slot, int* epoch_local, int which, bool* ok_shared) {
   __syncthreads();
   if (threadIdx.x == 0) {
+    // One system-scope fence publishes everything this block (and, through the barrier above, its threads) wrote;
+    // the flag stores that follow it can then be relaxed - a release per peer would repeat the fence world times.
     __threadfence_system();
     const int e = ++epoch_local[slot * 2 + which];
     bool ok = true;
     for (int r = 0; r < peers.world; ++r)
-      st_release_sys(peers.flags[r] + (which * kCommMaxBlocks + slot) * 8 + peers.rank, e);
+      st_relaxed_sys(peers.flags[r] + (which * kCommMaxBlocks + slot) * 8 + peers.rank, e);
     for (int r = 0; r < peers.world && ok; ++r)
       ok = wait_flag_ge(peers.flags[peers.rank] + (which * kCommMaxBlocks + slot) * 8 + r, e, peers.limit_ns, peers.status);
     *ok_shared = ok;

@@ -47,8 +47,11 @@ static void symm_free(int64_t ptr) { cudaFree(reinterpret_cast<void*>(ptr)); }
 static at::Tensor tensor_view(int64_t ptr, std::vector<int64_t> shape, const std::string& dtype, int64_t device) {
   at::ScalarType st = dtype == "bf16" ? at::kBFloat16 : dtype == "f32" ? at::kFloat : dtype == "i32" ? at::kInt
                     : dtype == "u8" ? at::kByte : at::kLong;
-  auto opts = at::TensorOptions().dtype(st).device(at::kCUDA, static_cast<c10::DeviceIndex>(device));
-  return at::from_blob(reinterpret_cast<void*>(ptr), shape, [](void*) {}, opts);
+  const c10::Device dev(at::kCUDA, static_cast<c10::DeviceIndex>(device));
+  auto opts = at::TensorOptions().dtype(st).device(dev);
+  // The target device is stated, not inferred from the pointer: a peer's memory mapped through the virtual-memory
+  // API reports the peer as its device, while every kernel that touches the view runs on this rank's device.
+  return at::from_blob(reinterpret_cast<void*>(ptr), shape, [](void*) {}, opts, dev);
 }
 
 class Comm {
