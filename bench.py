@@ -57,6 +57,9 @@ def parse():
                    help="bank gradient accumulation: full buffer per rank (default) or per-group reduce-scatter")
     p.add_argument("--nvls", action="store_true",
                    help="gradient reductions through the NVLink switch (multimem) instead of peer loads")
+    p.add_argument("--ddp-serial", action="store_true",
+                   help="data-parallel engine: one all-reduce after backward instead of per-bucket all-reduces beside it")
+    p.add_argument("--ddp-comm-blocks", type=int, default=16, help="grid cap of the overlapped bucket all-reduces")
     p.add_argument("--no-step-graph", action="store_true",
                    help="run forward/backward eagerly instead of replaying the captured micro-batch CUDA graphs")
     p.add_argument("--engine", type=str, default="fsdp", choices=["fsdp", "ddp"],
@@ -151,7 +154,7 @@ def run_ours(args):
                                grads=args.fsdp_grads, nvls=args.nvls)
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
-        engine = DataParallelEngine(model, nvls=args.nvls)
+        engine = DataParallelEngine(model, nvls=args.nvls, overlap=not args.ddp_serial, comm_blocks=args.ddp_comm_blocks)
     ns = argparse.Namespace(lr=LR if args.optimizer != "adamw" else 1e-3, weight_decay=WD, tile_size=args.tile, cuda_graph=True,
                             cuda_graph_warmup=1)
     optimizer = get_optimizer(args.optimizer, model, ns)
@@ -223,7 +226,7 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model, "global_batch": args.micro_batch * args.grad_acc * world,
                        "seq_len": args.seq_len, "micro_batch_per_gpu": args.micro_batch, "grad_acc": args.grad_acc,
-                       "parallelism": (f"fsdp-banks{world}" + (f" weights={engine.weights_mode} grads={engine.grads_mode}" + (" nvls" if engine.nvls else "") if world > 1 else "")) if args.engine == "fsdp" else f"dp{world}",
+                       "parallelism": (f"fsdp-banks{world}" + (f" weights={engine.weights_mode} grads={engine.grads_mode}" + (" nvls" if engine.nvls else "") if world > 1 else "")) if args.engine == "fsdp" else f"dp{world}" + ("" if world == 1 else (" serial all-reduce" if args.ddp_serial else " overlapped bucket all-reduce")),
                        "optimizer": f"{args.optimizer} tile {args.tile}, lr {ns.lr}, wd {WD}, cuda graph",
                        "forward_backward": "eager" if args.no_step_graph else "micro-batch CUDA graphs (public Trainer option)",
                        "activation_checkpointing": checkpointing,

@@ -292,10 +292,12 @@ class ShardedEngine:
         """Bank slots ``idx .. idx+n`` as an ``(n, H, W)`` tensor from wherever this mode keeps them: the gathered
         copy, the owner's shard (own layers; or, in peer mode, seen through the peer mapping, which only this
         package's own TMA GEMMs ever read) or the staging slot of the layer's group."""
+        owner, loc = self._place(st, idx)
         if st.gathered is not None:
+            if owner == self.rank and st.gathered is not st.shard:
+                return st.shard[loc:loc + n]          # own layers are read in place; the re-gather skips them
             p = self._phys(st, idx)
             return st.gathered[p:p + n]
-        owner, loc = self._place(st, idx)
         if st.ring is None:
             return st.peer_shards[owner][loc:loc + n]
         if owner == self.rank:
@@ -510,14 +512,14 @@ class ShardedEngine:
         if self.gather_blocks <= 0:
             # Copy engines (measured 0.94 of the peer-copy rate against 0.55 for the SM copy kernel at two ranks):
             # one copy per (owner, bank), owners in the order rank+1, rank+2, ... so that every owner serves one
-            # reader at a time.  The own shard is a local copy.
-            for j in range(self.world):
+            # reader at a time.  Own layers are read from the shard itself (see _weights), so nothing is copied for them.
+            for j in range(1, self.world):
                 r = (self.rank + j) % self.world
                 for st in self.state.values():
                     if st.gathered is None:
                         continue
                     H, W = st.spec.matrix_shape
-                    src = st.shard if r == self.rank else self.heap.view(r, st.shard_off, (st.n_local, H, W), self.dtype)
+                    src = self.heap.view(r, st.shard_off, (st.n_local, H, W), self.dtype)
                     st.gathered[r * st.n_local:(r + 1) * st.n_local].copy_(src, non_blocking=True)
             return
         if self._copy_table is None:                 # gather_blocks > 0: the multi_copy kernel on that many blocks
