@@ -309,7 +309,9 @@ class ShardedEngine:
 
     def linear(self, x, bank_name: str, idx: int, bias=None):
         st = self.state[bank_name]
-        if st.ring is not None:          # staged weights are looked up again in backward, not saved by autograd
+        if self.world > 1:
+            # Looked up again in backward, not saved by autograd: staged weights come and go between the two passes,
+            # and own layers are views of the heap-resident shard, whose version counter other heap writes may share.
             y = ops.linear(x, None, sink=st.sinks[idx], w_getter=lambda: self._weights(st, idx, 1)[0])
         else:
             y = ops.linear(x, self._weights(st, idx, 1)[0], sink=st.sinks[idx])
@@ -319,7 +321,7 @@ class ShardedEngine:
         """Slots ``idx`` and ``idx+1`` applied as one ``(2H, W)`` projection (one GEMM in each direction)."""
         st = self.state[bank_name]
         H, W = st.spec.matrix_shape
-        if st.ring is not None:
+        if self.world > 1:
             return ops.linear(x, None, sink=st.pair_sinks[idx],
                               w_getter=lambda: self._weights(st, idx, 2).view(2 * H, W))
         return ops.linear(x, self._weights(st, idx, 2).view(2 * H, W), sink=st.pair_sinks[idx])
