@@ -91,6 +91,9 @@ def scenario_train(mode, optimizer_name, device):
     # half empty), so the ring rotates and a pad layer takes part
     mode, *opts = mode.split(":")
     layers = 5 if opts else 3
+    for o in opts:                         # "L20": a deeper model, so that many ranks still see several layer groups
+        if o[:1] == "L" and o[1:].isdigit():
+            layers = int(o[1:])
     model = CausalLM(_cfg(layers)).to(device, torch.bfloat16)
     if "ckpt" in opts:
         model.gradient_checkpointing_enable()

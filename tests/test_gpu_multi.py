@@ -64,6 +64,16 @@ def test_multi_gpu_training_matches_single_process(mode, opt):
     assert "PARITY OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
 
 
+@pytest.mark.skipif(N_GPUS < 4, reason="needs at least 4 GPUs")
+@pytest.mark.parametrize("mode,opt", [("fsdp:ring:sharded:L20", "adamw"), ("fsdp:ring:replicated:graph:L20", "himuon"),
+                                      ("fsdp:gathered:replicated:L20", "himuon")])
+def test_many_rank_training_matches_single_process(mode, opt):
+    """All GPUs of the machine (up to 8): 20 layers are three layer groups on 8 ranks (five on 4), the last one partly
+    made of pad layers, and every rank owns at most three layers of each bank."""
+    r = _run(min(N_GPUS, 8), "train", mode, opt, timeout=900)
+    assert "PARITY OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
 @needs2
 def test_missing_rank_surfaces_as_status_not_hang():
     r = _run(2, "timeout", "-", "-", timeout=300)
