@@ -37,6 +37,9 @@ def scenario_train(mode, optimizer_name):
     # one half empty, so the ring rotates and a pad layer takes part
     mode, *opts = mode.split(":")
     layers = 5 if opts else 3
+    for o in opts:                         # "L7": another depth
+        if o[:1] == "L" and o[1:].isdigit():
+            layers = int(o[1:])
     model = CausalLM(_cfg(layers))
     if "ckpt" in opts:
         model.gradient_checkpointing_enable()
@@ -45,7 +48,8 @@ def scenario_train(mode, optimizer_name):
         engine = ShardedEngine(model, use_banks=True, weights=opts[0] if opts else None,
                                grads=opts[1] if len(opts) > 1 else "replicated", debug="debug" in opts)
         if opts and world > 1:
-            assert engine.weights_mode == opts[0] and engine.grads_mode == opts[1] and engine.uses_fences
+            assert engine.weights_mode == opts[0] and engine.grads_mode == opts[1]
+            assert engine.uses_fences == (opts[0] == "ring" or opts[1] == "sharded")
             b = engine.bank_bytes()
             # this rank holds its 1/world share plus the staging slots, not the whole banks
             groups = engine.n_groups

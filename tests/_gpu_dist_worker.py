@@ -106,7 +106,8 @@ def scenario_train(mode, optimizer_name, device):
         if mode == "fsdp-peer":
             assert any(st.gathered is None for st in engine.state.values()) or world == 1
         if opts and world > 1:
-            assert engine.weights_mode == opts[0] and engine.grads_mode == opts[1] and engine.uses_fences
+            assert engine.weights_mode == opts[0] and engine.grads_mode == opts[1]
+            assert engine.uses_fences == (opts[0] == "ring" or opts[1] == "sharded")
             b, groups = engine.bank_bytes(), engine.n_groups
             # per-rank bytes: the 1/world share plus the staging slots, not the whole banks
             if opts[0] == "ring":

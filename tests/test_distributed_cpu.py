@@ -24,7 +24,8 @@ def _run(nproc, *argv, timeout=300):
                                             ("fsdp", "himuon", 4), ("fsdp", "adamw", 2),
                                             ("fsdp:ring:replicated", "himuon", 2), ("fsdp:gathered:sharded", "himuon", 2),
                                             ("fsdp:ring:sharded:ckpt:debug", "himuon", 2), ("fsdp:ring:sharded", "adamw", 2),
-                                            ("fsdp:ring:sharded", "muon-fsdp", 3), ("ddp:overlap", "adamw", 2)])
+                                            ("fsdp:ring:sharded", "muon-fsdp", 3), ("ddp:overlap", "adamw", 2),
+                                            ("fsdp:gathered:replicated:L7", "himuon", 4), ("fsdp:ring:sharded:L7", "himuon", 3)])
 def test_multi_rank_training_matches_single_process(mode, opt, nproc):
     r = _run(nproc, "train", mode, opt)
     assert "PARITY OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
