@@ -111,3 +111,19 @@ def test_symmetric_heap_guard_zones_catch_an_overrun():
     plain = SymmetricHeap(1 << 12, torch.device("cpu"))
     plain.alloc((8,), torch.float32)
     assert plain.check_canaries() == []
+
+
+def test_phase_timer_is_inert_without_cuda_and_ranges_nest():
+    from himuon_b200.utils import PhaseTimer, nvtx_range
+
+    t = PhaseTimer(enabled=True)            # no CUDA here: stays disabled, costs nothing
+    with t.phase("forward_backward"):
+        with nvtx_range("inner"):
+            pass
+    with t.phase("optimizer"):
+        pass
+    import torch
+    if not torch.cuda.is_available():
+        assert t.enabled is False and t.summary() == {}
+    t.reset()
+    assert t.summary() == {}
