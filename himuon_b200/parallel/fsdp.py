@@ -178,6 +178,10 @@ class ShardedEngine:
                 st.gathered = torch.zeros(n_phys, H, W, device=self.device, dtype=self.dtype)
                 for s in range(b.spec.n_logical):
                     st.gathered[self._phys(st, s)].copy_(full.data[s])
+                if self.cuda:
+                    st.peer_shards = [st.shard if r == self.rank else
+                                      self.heap.view(r, st.shard_off, (st.n_local, H, W), self.dtype)
+                                      for r in range(self.world)]
             param = nn.Parameter(st.shard, requires_grad=True)
             param._bank_spec = b.spec
             # pad slots (layers past the model's depth) hold zeros and need no optimizer work
@@ -199,14 +203,20 @@ class ShardedEngine:
         if self.cuda:
             torch.cuda.empty_cache()
         object.__setattr__(model, "_bank_engine", self if self.banks is not None else None)
-        object.__setattr__(model, "_layer_hooks", self if self.uses_fences else None)
+        # Gathered copy on CUDA: the once-per-step re-gather is deferred to the next forward pass and issued group by
+        # group on the copy stream, so that all but the first group's copies run beside the first micro-batch.
+        self._overlap_regather = self.cuda and self.world > 1 and self.banks is not None and weights == "gathered" \
+            and gather_blocks <= 0
+        self._regather_pending = False
+        self._group_ready: dict[int, object] = {}
+        object.__setattr__(model, "_layer_hooks", self if (self.uses_fences or self._overlap_regather) else None)
         self.materialize_grads = False    # True: produce .grad for bank shards (optimizers without the fused path)
         self._copy_table = None
         self._offload = None
         # staging-ring bookkeeping (host side; it describes the work enqueued so far, in program order)
         self._slot_group = [None, None]
         self._slot_ready = [None, None]
-        self._copy_stream = torch.cuda.Stream(self.device) if (self.cuda and weights == "ring") else None
+        self._copy_stream = torch.cuda.Stream(self.device) if (self.cuda and self.world > 1 and weights in ("ring", "gathered")) else None
         self.ring_fetches = 0             # groups copied so far (tests, diagnostics)
         self.group_reductions = 0
         if self.world > 1:
@@ -294,6 +304,9 @@ class ShardedEngine:
         package's own TMA GEMMs ever read) or the staging slot of the layer's group."""
         owner, loc = self._place(st, idx)
         if st.gathered is not None:
+            if self._regather_pending:               # a caller outside the decoder's layer loop: gather everything now
+                self._start_regather()
+                self._wait_all_groups()
             if owner == self.rank and st.gathered is not st.shard:
                 return st.shard[loc:loc + n]          # own layers are read in place; the re-gather skips them
             p = self._phys(st, idx)
@@ -334,9 +347,17 @@ class ShardedEngine:
     def pre_layer(self, i: int, h, delta):
         """Before decoder layer ``i``: at the first layer of a group make the group's weights available and start
         fetching the next group."""
-        if not self.uses_fences or i % self.world:
+        if i % self.world:
             return h, delta
         g = i // self.world
+        if self._overlap_regather:
+            if i == 0 and self._regather_pending:
+                self._start_regather()
+            ready = self._group_ready.pop(g, None)
+            if ready is not None:
+                torch.cuda.current_stream(self.device).wait_event(ready)
+        if not self.uses_fences:
+            return h, delta
         if i == 0:
             self._begin_pass()
         if self.weights_mode == "ring":
@@ -354,6 +375,35 @@ class ShardedEngine:
         if torch.is_grad_enabled() and h.requires_grad:
             h, delta = _GroupFence.apply(self, "end", i // self.world, h, delta)
         return h, delta
+
+    def _start_regather(self):
+        """Gathered mode, after an optimizer step: all owners have updated their shards (barrier), then the copy engines
+        pull the peers' layers group by group on the copy stream; the forward pass waits group by group, so only the
+        first group's copies are exposed.  Runs eagerly or as part of the captured first micro-batch of a step."""
+        self._regather_pending = False
+        self.heap.barrier()
+        ops._count()
+        main = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(main)
+        self._group_ready = {}
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(start)
+            for g in range(self.n_groups):
+                for j in range(1, self.world):
+                    owner = (self.rank + j) % self.world
+                    for st in self.state.values():
+                        lo = owner * st.n_local + g * st.unit
+                        st.gathered[lo:lo + st.unit].copy_(st.peer_shards[owner][g * st.unit:(g + 1) * st.unit], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self._copy_stream)
+                self._group_ready[g] = ev
+
+    def _wait_all_groups(self):
+        main = torch.cuda.current_stream(self.device)
+        for ev in self._group_ready.values():
+            main.wait_event(ev)
+        self._group_ready = {}
 
     def _begin_pass(self):
         """A new forward pass.  Group-staged gradient sinks start by overwriting.  The weight staging slots keep what
@@ -481,8 +531,12 @@ class ShardedEngine:
     def zero_grad(self, set_to_none: bool = False):
         """Runs after ``optimizer.step()``: refresh the gathered working copy and reset the accumulators."""
         if self.world > 1:
-            self.heap.barrier()                    # every owner has finished updating its shards
-            self._regather()
+            if self._overlap_regather:
+                self._wait_all_groups()            # leftovers of a forward pass that stopped early
+                self._regather_pending = True      # barrier + copies happen at the start of the next forward pass
+            else:
+                self.heap.barrier()                # every owner has finished updating its shards
+                self._regather()
         for flat, _ in self.regions:
             flat.zero_()
         for st in self.state.values():

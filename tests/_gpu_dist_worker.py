@@ -108,6 +108,7 @@ def scenario_train(mode, optimizer_name, device):
         if opts and world > 1:
             assert engine.weights_mode == opts[0] and engine.grads_mode == opts[1]
             assert engine.uses_fences == (opts[0] == "ring" or opts[1] == "sharded")
+            assert engine._overlap_regather == (opts[0] == "gathered")
             b, groups = engine.bank_bytes(), engine.n_groups
             # per-rank bytes: the 1/world share plus the staging slots, not the whole banks
             if opts[0] == "ring":
