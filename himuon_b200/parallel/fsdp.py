@@ -11,9 +11,12 @@ the layer axis in whole matrices, so the optimizer needs no collective (the refe
   matrices per bank and four own 4, instead of seven owning 5 and one owning 1).
 * **Weights: gathered copy or staging ring** (``weights=``).
 
-  - ``"gathered"``: every rank keeps a full bf16 working copy of every bank, refreshed after each optimizer step by
-    copy-engine pulls of the peers' shards over NVLink (``gather_blocks > 0`` selects the ``multi_copy`` kernel on that
-    many blocks instead); accumulation micro-steps do no parameter communication (180 GB of HBM hold the copy).
+  - ``"gathered"``: every rank keeps a full bf16 working copy of the peers' layers (its own layers are read from the
+    shard itself), refreshed once per optimizer step by copy-engine pulls over NVLink.  The refresh is deferred to the
+    start of the next forward pass and issued layer group by layer group on a side stream, and the forward pass waits
+    group by group, so all but the first group's copies run beside the first micro-batch (``gather_blocks > 0``
+    selects one ``multi_copy`` kernel launch right after the optimizer step instead).  Accumulation micro-steps do no
+    parameter communication (180 GB of HBM hold the copy).
   - ``"ring"``: no full copy.  Layers are taken in groups of ``world`` consecutive layers (one per owner); two
     group-sized staging slots rotate.  While group ``g`` computes, a side stream copies group ``g+1`` (``g-1`` in
     backward) from the owners' shards with the copy engines - no SM is taken from the GEMMs, and rank ``r`` visits
