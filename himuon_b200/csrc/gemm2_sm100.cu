@@ -69,44 +69,6 @@ __device__ __forceinline__ void tma2_load_3d(void* smem_dst, const CUtensorMap* 
 constexpr int BN2 = 256;     // tile width
 constexpr int BNH = 128;     // rows of B staged by each CTA
 
-// Last step of a split last-wave tile, run by the 128 epilogue threads of the CTA that delivered the final K-slice of
-// one half (128 rows x 256 columns) of the tile: the complete fp32 sums in the scratch half `ws` become outputs (alpha,
-// beta*aux, optional bf16 rounding point, cast) and the scratch is left zeroed for the next launch.
-__device__ __forceinline__ void finish_tail_half(const GemmDev& p, float* __restrict__ ws, int b, int m0, int n0, int t) {
-  constexpr int GROUPS = BM * BN2 / 4;                      // float4 groups of the half tile
-#pragma unroll 4
-  for (int i = t; i < GROUPS; i += 128) {
-    const int r = i >> 6, c = (i & 63) * 4;
-    float4* src = reinterpret_cast<float4*>(ws + r * BN2 + c);
-    const float4 v = __ldcg(src);
-    __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
-    const int row = m0 + r, col = n0 + c;
-    if (row >= p.M || col >= p.N) continue;
-    const float vals[4] = {v.x, v.y, v.z, v.w};
-    const long long c_off = static_cast<long long>(b) * p.strideC + static_cast<long long>(row) * p.ldc + col;
-    const long long x_off = static_cast<long long>(b) * p.strideAux + static_cast<long long>(row) * p.ldaux + col;
-    float o[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      o[j] = p.alpha * vals[j];
-      if (p.aux != nullptr && col + j < p.N) {
-        if (p.round_acc) o[j] = round_bf16(o[j]);
-        o[j] += p.beta * (p.out_fp32 ? reinterpret_cast<const float*>(p.aux)[x_off + j]
-                                     : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.aux)[x_off + j]));
-      }
-    }
-    if (col + 4 <= p.N) {                                  // N and ldc are multiples of 4 for TMA-storable outputs
-      if (p.out_fp32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.C) + c_off) = make_float4(o[0], o[1], o[2], o[3]);
-      else *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.C) + c_off) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
-    } else {
-      for (int j = 0; j < 4 && col + j < p.N; ++j) {
-        if (p.out_fp32) reinterpret_cast<float*>(p.C)[c_off + j] = o[j];
-        else reinterpret_cast<__nv_bfloat16*>(p.C)[c_off + j] = __float2bfloat16_rn(o[j]);
-      }
-    }
-  }
-}
-
 template <int STAGES, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -126,7 +88,6 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* last_flag = abort_flag + 1;       // split tail: this CTA delivered the last K-slice of a tile half
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -259,28 +220,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(acc * BN2);
       const long long aux_row = static_cast<long long>(b) * p.strideAux + static_cast<long long>(m0 + row_in_tile) * p.ldaux;
       if (w.split) {
-        // K-slice of a last-wave tile: add the fp32 partial into the scratch tile (rows tail*256 + rank*128 ..).
-        // Whichever CTA delivers the last slice of a tile half turns the complete sums into the output (no CTA ever
-        // waits for another one: every slice just counts itself in after its reduction has landed).
+        // K-slice of a last-wave tile: add the fp32 partial into the scratch tile (rows tail*256 + rank*128 ..);
+        // a follow-up kernel applies the epilogue to the complete sums
         epilogue_tile_tma<BN2, true>(&tmW, sC, t_acc, row_in_tile, w.tail * 2 * BM + static_cast<int>(rank) * BM, 0, 0, nullptr, 0,
                                      1 << 30, BN2, 1.f, 0.f, 0, slab_seq, issuer, true);
-        int* counter = p.tail_count + w.tail * 2 + static_cast<int>(rank);
-        if (issuer) {
-          tma_store_wait_all();                    // this slice's sums are in the scratch tile, not just read from smem
-          __threadfence();
-          const int arrived = atomicAdd(counter, 1);
-          if (arrived == p.nslices - 1) __threadfence();
-          *last_flag = (arrived == p.nslices - 1) ? 1 : 0;
-        }
-        named_barrier(3, 128);
-        if (*last_flag) {
-          finish_tail_half(p, p.tail_ws + (static_cast<long long>(w.tail) * 2 * BM + static_cast<long long>(rank) * BM) * BN2,
-                           b, m0, nt * BN2, threadIdx.x - 128);
-          named_barrier(3, 128);                   // every thread has read the flag and finished its share
-          if (issuer) *counter = 0;                // ready for the next launch
-        } else {
-          named_barrier(3, 128);
-        }
       } else if (m0 < p.M) {              // uniform: the second CTA of a ragged last row block has nothing to store
         if (p.reduce_out && p.out_fp32)   // C += alpha*acc without reading C: the L2 adds the staged slabs
           epilogue_tile_tma<BN2, true>(&tmC, sC, t_acc, row_in_tile, m0, nt * BN2, b, nullptr, 0, p.M, p.N, p.alpha,
@@ -313,11 +256,51 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
-// fp32 scratch for the split-K tail of the pair kernel: up to kPairTailMax tiles of 256 x 256, followed by one arrival
-// counter per (tile, CTA of the pair); all zero between launches.  One buffer per device, shared by every GEMM of
-// that device (GEMMs that split must not overlap on different streams).
+// Second half of the split-K tail: turns the complete fp32 sums of the last-wave tiles into outputs (alpha, beta*aux,
+// optional bf16 rounding point, cast) and leaves the scratch zeroed for the next launch.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gemm2_finish_kernel(float* __restrict__ ws, GemmDev p, int first_tail_tile, int n_tail) {
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const long long per_tile = 256LL * 256 / 4;            // float4 groups per tile
+  const long long total = per_tile * n_tail;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / per_tile);
+    const int e = static_cast<int>(i - t * per_tile);
+    const int r = e >> 6, c = (e & 63) * 4;
+    float4* src = reinterpret_cast<float4*>(ws + (static_cast<long long>(t) * 256 + r) * 256 + c);
+    const float4 v = *src;
+    *src = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int tile = first_tail_tile + t;
+    const int b = tile / tiles_per_batch;
+    const int rr = tile - b * tiles_per_batch;
+    const int row = (rr % p.tiles_m) * 256 + r;
+    const int col = (rr / p.tiles_m) * 256 + c;
+    if (row >= p.M) continue;
+    const float vals[4] = {v.x, v.y, v.z, v.w};
+    T* cp = reinterpret_cast<T*>(p.C) + static_cast<long long>(b) * p.strideC + static_cast<long long>(row) * p.ldc + col;
+    const T* xp = p.aux ? reinterpret_cast<const T*>(p.aux) + static_cast<long long>(b) * p.strideAux +
+                              static_cast<long long>(row) * p.ldaux + col
+                        : nullptr;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (col + j >= p.N) break;
+      float o = p.alpha * vals[j];
+      if (xp) {
+        if (p.round_acc) o = round_bf16(o);
+        if (sizeof(T) == 2) o += p.beta * __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(xp)[j]);
+        else o += p.beta * reinterpret_cast<const float*>(xp)[j];
+      }
+      if (sizeof(T) == 2) reinterpret_cast<__nv_bfloat16*>(cp)[j] = __float2bfloat16_rn(o);
+      else reinterpret_cast<float*>(cp)[j] = o;
+    }
+  }
+}
+
+// fp32 scratch for the split-K tail of the pair kernel: up to kPairTailMax tiles of 256 x 256, zero between launches.
+// One buffer per device, shared by every GEMM of that device (GEMMs that split must not overlap on different streams).
 constexpr int kPairTailMax = 40;
-constexpr size_t kPairScratchBytes = static_cast<size_t>(kPairTailMax) * 256 * 256 * sizeof(float);
 static float* pair_scratch() {
   static float* per_device[64] = {nullptr};
   int dev = 0;
@@ -325,7 +308,7 @@ static float* pair_scratch() {
   if (dev < 0 || dev >= 64) dev = 0;
   if (per_device[dev] == nullptr) {
     void* ptr = nullptr;
-    const size_t bytes = kPairScratchBytes + 2 * kPairTailMax * sizeof(int);
+    const size_t bytes = static_cast<size_t>(kPairTailMax) * 256 * 256 * sizeof(float);
     if (cudaMalloc(&ptr, bytes) == cudaSuccess && cudaMemset(ptr, 0, bytes) == cudaSuccess) per_device[dev] = static_cast<float*>(ptr);
     else cudaGetLastError();
   }
@@ -398,7 +381,7 @@ static void launch_gemm2(const GemmArgs& a, cudaStream_t stream) {
   int cap = max_pairs;
   if (a.max_ctas > 0 && a.max_ctas / 2 < cap) cap = a.max_ctas / 2 > 0 ? a.max_ctas / 2 : 1;
   // Split the tiles of a mostly idle last wave along K: each K-slice adds its fp32 partial tile into a scratch tile
-  // with TMA reductions and the CTA that delivers the last slice applies the epilogue.
+  // with TMA reductions and a small follow-up kernel applies the epilogue.
   CUtensorMap tmW = tmC;
   const int rem = static_cast<int>(total % cap);
   float* scratch = nullptr;
@@ -410,11 +393,9 @@ static void launch_gemm2(const GemmArgs& a, cudaStream_t stream) {
       (scratch = pair_scratch()) != nullptr) {
     int sl = cap / rem;
     if (sl > p.kblocks / 8) sl = p.kblocks / 8;
-    // worth it only when the K-blocks saved outweigh the fp32 reduction traffic
+    // worth it only when the K-blocks saved outweigh the fp32 reduction traffic and the second launch (~12 us)
     if (sl >= 2 && (sl - 1) * p.kblocks / sl >= 40) {
       p.nslices = sl;
-      p.tail_ws = scratch;
-      p.tail_count = reinterpret_cast<int*>(reinterpret_cast<char*>(scratch) + kPairScratchBytes);
       p.full_items = static_cast<int>(total) - rem;
       p.total_items = p.full_items + rem * sl;
       const uint64_t dimsW[3] = {256, static_cast<uint64_t>(kPairTailMax) * 256, 1};
@@ -429,6 +410,12 @@ static void launch_gemm2(const GemmArgs& a, cudaStream_t stream) {
     pairs = cap;
   }
   kern<<<static_cast<int>(2 * pairs), 256, SMEM, stream>>>(tmA, tmB, tmC, tmW, p);
+  if (p.nslices > 1) {
+    const long long groups = 256LL * 256 / 4 * rem;
+    const int blocks = static_cast<int>((groups + 255) / 256 < num_sms() * 4 ? (groups + 255) / 256 : num_sms() * 4);
+    if (a.out_fp32) gemm2_finish_kernel<float><<<blocks, 256, 0, stream>>>(scratch, p, p.full_items, rem);
+    else gemm2_finish_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(scratch, p, p.full_items, rem);
+  }
 }
 
 // True when the pair kernel can run this problem and is expected to win: TMA-storable output, more than one CTA

@@ -27,9 +27,6 @@ struct GemmDev {
   // tiles that lie entirely above the diagonal are not computed; tiles entirely below it are also stored transposed.
   int sym;          // 1: symmetric mode
   int sym_tiles;    // computed tiles per batch entry
-  // Split tail of the pair kernel: fp32 scratch tiles and one arrival counter per (tail tile, CTA of the pair).
-  float* tail_ws;
-  int* tail_count;
   int* status;
 };
 
