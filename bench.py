@@ -55,6 +55,9 @@ def parse():
                    help="bank working copy: full gathered copy (default), two-slot staging ring, or peer reads")
     p.add_argument("--fsdp-grads", type=str, default="replicated", choices=["replicated", "sharded"],
                    help="bank gradient accumulation: full buffer per rank (default) or per-group reduce-scatter")
+    p.add_argument("--no-grad-prefetch", action="store_true",
+                   help="sharded engine: leave the peers' gradient replicas to momentum_tile's peer loads instead of "
+                        "pulling them with the copy engines during the last micro-batch's backward pass")
     p.add_argument("--nvls", action="store_true",
                    help="gradient reductions through the NVLink switch (multimem) instead of peer loads")
     p.add_argument("--ddp-serial", action="store_true",
@@ -151,7 +154,8 @@ def run_ours(args):
     if args.engine == "fsdp":
         weights = "peer" if args.peer_weights else args.fsdp_weights
         engine = ShardedEngine(model, use_banks=args.optimizer in ("himuon", "muon-fsdp", "adamw"), weights=weights,
-                               grads=args.fsdp_grads, nvls=args.nvls)
+                               grads=args.fsdp_grads, nvls=args.nvls,
+                               grad_prefetch=False if args.no_grad_prefetch else None)
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
         engine = DataParallelEngine(model, nvls=args.nvls, overlap=not args.ddp_serial, comm_blocks=args.ddp_comm_blocks)
@@ -208,14 +212,17 @@ def run_ours(args):
         e2e = {"value": tokens_per_step * args.steps / (ms_e2e / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": trainer.h2d_bytes // args.steps, "d2h_bytes_per_step": trainer.d2h_bytes // args.steps,
                "ms_per_step": ms_e2e / args.steps, "last_loss": losses[-1]}
-    # Where a step goes: device time per phase (CUDA events, max over ranks) over two more steps, outside the timed
-    # regions.  grad_reduce + regather_reset is the communication that is not hidden behind compute.
+    # Where a step goes: device time per phase (CUDA events) over two more steps, outside the timed regions, as the
+    # maximum and the minimum over ranks.  grad_reduce and regather_reset wait for the other ranks, so their maximum
+    # holds the time the fastest rank waited for the slowest (already counted in the slowest rank's forward_backward)
+    # and their minimum, seen by the rank that arrived last, is the communication not hidden behind compute.
     from himuon_b200.utils import PhaseTimer
     trainer.phases = PhaseTimer(True, device)
     n_phase = 2
     for i in range(n_phase):
         trainer.train_step(dev_batches[args.warmup + (i % args.steps)])
     phases = {k: round(v / n_phase, 3) for k, v in trainer.phases.summary().items()}
+    phases_min = {k: round(v / n_phase, 3) for k, v in trainer.phases.summary(reduce="min").items()}
     trainer.phases = PhaseTimer(False)
     ops.check_status()
     if rank == 0:
@@ -226,13 +233,15 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model, "global_batch": args.micro_batch * args.grad_acc * world,
                        "seq_len": args.seq_len, "micro_batch_per_gpu": args.micro_batch, "grad_acc": args.grad_acc,
-                       "parallelism": (f"fsdp-banks{world}" + (f" weights={engine.weights_mode} grads={engine.grads_mode}" + (" nvls" if engine.nvls else "") if world > 1 else "")) if args.engine == "fsdp" else f"dp{world}" + ("" if world == 1 else (" serial all-reduce" if args.ddp_serial else " overlapped bucket all-reduce")),
+                       "parallelism": (f"fsdp-banks{world}" + (f" weights={engine.weights_mode} grads={engine.grads_mode}" + (" nvls" if engine.nvls else "") + (" grad-prefetch" if engine.grad_prefetch else "") if world > 1 else "")) if args.engine == "fsdp" else f"dp{world}" + ("" if world == 1 else (" serial all-reduce" if args.ddp_serial else " overlapped bucket all-reduce")),
                        "optimizer": f"{args.optimizer} tile {args.tile}, lr {ns.lr}, wd {WD}, cuda graph",
                        "forward_backward": "eager" if args.no_step_graph else "micro-batch CUDA graphs (public Trainer option)",
                        "activation_checkpointing": checkpointing,
                        "l2": "no flush: each step streams >8 GB of weights and activations (L2 is 126 MB)"},
             "optimizer_step_ms": opt_ms, "phases_ms_per_step": phases,
-            "exposed_comm_ms_per_step": round(phases.get("grad_reduce", 0.0) + phases.get("regather_reset", 0.0), 3),
+            "phases_min_over_ranks_ms_per_step": phases_min,
+            "exposed_comm_ms_per_step": round(phases_min.get("grad_reduce", 0.0) + phases_min.get("regather_reset", 0.0), 3),
+            "rank_skew_ms_per_step": round(phases.get("grad_reduce", 0.0) - phases_min.get("grad_reduce", 0.0), 3),
             "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": launches, "impl": "ours",
         }
         print(json.dumps(out), flush=True)

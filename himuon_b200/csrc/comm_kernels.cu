@@ -68,14 +68,17 @@ __device__ __forceinline__ bool block_handshake(CommPeers peers, int slot, int* 
   return *ok_shared;
 }
 
-__global__ void peer_barrier_kernel(CommPeers peers, int* epoch_local) {
+// The barrier owns the last block slot (no collective's grid reaches it).  Its two phases are two independent
+// channels with their own flags and epoch counters: channel 0 for barriers on the stream that also runs the other
+// collectives, channel 1 for barriers on a side stream whose order against channel 0 differs from rank to rank.
+__global__ void peer_barrier_kernel(CommPeers peers, int* epoch_local, int channel) {
   __shared__ bool ok;
-  block_handshake(peers, kCommMaxBlocks - 1, epoch_local, 0, &ok);
+  block_handshake(peers, kCommMaxBlocks - 1, epoch_local, channel, &ok);
 }
 
-void peer_barrier(const CommPeers& peers, int* epoch_local, cudaStream_t s) {
+void peer_barrier(const CommPeers& peers, int* epoch_local, cudaStream_t s, int channel) {
   if (peers.world <= 1) return;
-  peer_barrier_kernel<<<1, 32, 0, s>>>(peers, epoch_local);
+  peer_barrier_kernel<<<1, 32, 0, s>>>(peers, epoch_local, channel & 1);
 }
 
 // ------------------------------------------------------------------------------------------------ all-reduce

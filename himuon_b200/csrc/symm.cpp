@@ -76,7 +76,7 @@ class Comm {
   int64_t peer_ptr(int r) const { return heaps_.at(r); }
   static int64_t flag_bytes() { return kCommFlagBytes; }
 
-  void barrier() { peer_barrier(peers_, epoch_, at::cuda::getCurrentCUDAStream().stream()); }
+  void barrier(int channel) { peer_barrier(peers_, epoch_, at::cuda::getCurrentCUDAStream().stream(), channel); }
 
   // In-place all-reduce of the same heap region on every rank.
   void allreduce(int64_t offset_bytes, int64_t n_elems, bool fp32, double scale, int64_t max_blocks, int64_t algo) {
@@ -138,7 +138,7 @@ void bind_symm(py::module_& m) {
       .def("set_timeout", &Comm::set_timeout)
       .def("peer_ptr", &Comm::peer_ptr)
       .def_static("flag_bytes", &Comm::flag_bytes)
-      .def("barrier", &Comm::barrier)
+      .def("barrier", &Comm::barrier, py::arg("channel") = 0)
       .def("allreduce", &Comm::allreduce, py::arg("offset_bytes"), py::arg("n_elems"), py::arg("fp32"), py::arg("scale"),
            py::arg("max_blocks") = 0, py::arg("algo") = 0)
       .def("reduce_to", &Comm::reduce_to, py::arg("offset_bytes"), py::arg("out"), py::arg("scale"), py::arg("beta") = 0.0,

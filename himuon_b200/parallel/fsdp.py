@@ -31,6 +31,11 @@ the layer axis in whole matrices, so the optimizer needs no collective (the refe
     GEMMs' epilogues; the owner sums the ``world`` replicas once per step, inside HiMuon's ``momentum_tile`` kernel
     through peer pointers (other optimizers: one ``reduce_replicas`` launch per bank).  This is what FSDP2 does under
     gradient accumulation too (unsharded gradients accumulate locally, one reduce-scatter per optimizer step).
+    With HiMuon on CUDA the peers' replicas of a rank's layers do not wait for the optimizer step (``grad_prefetch``):
+    in the last micro-batch of a step, whenever the backward pass leaves a layer group, a side stream meets the
+    other ranks at a barrier of its own and lets the copy engines pull the peers' finished gradients of this rank's
+    layer of the group into local staging buffers, beside the backward GEMMs of the earlier layers;
+    ``momentum_tile`` then sums local buffers only and the optimizer step moves nothing over NVLink.
   - ``"sharded"``: no full-bank buffer.  The weight gradients of one layer group land in a group-sized staging
     buffer; when the backward pass leaves the group, every owner sums its layer over the ranks (peer loads) straight
     into its own ``(n_local, H, W)`` accumulator.  Per-rank gradient memory is ``1/world`` of the banks plus one
@@ -66,7 +71,7 @@ class _BankState:
 class ShardedEngine:
     def __init__(self, model: nn.Module, use_banks: bool = True, cpu_offload: bool = False, timeout_s: float = 120.0,
                  gather_blocks: int = 0, peer_weights: bool = False, weights: str | None = None,
-                 grads: str = "replicated", nvls: bool = False, debug: bool = False):
+                 grads: str = "replicated", nvls: bool = False, debug: bool = False, grad_prefetch: bool | None = None):
         """``weights``: ``"gathered"`` (default), ``"ring"`` or ``"peer"`` (``peer_weights=True`` is the older spelling
         of the last); ``grads``: ``"replicated"`` (default) or ``"sharded"``; see the module docstring.
         ``nvls``: bind the symmetric heap to an NVLink multicast object; the gradient reductions onto the owners then
@@ -75,11 +80,22 @@ class ShardedEngine:
         ``debug``: race / overrun checks for development - guard zones after every heap region (``heap.check_canaries()``,
         verified in ``zero_grad``), and staging slots and group gradient buffers are filled with NaN whenever their
         contents become stale, so a kernel that reads a slot before its copy has landed poisons the loss visibly.
+        ``grad_prefetch``: pull the peers' gradient replicas of this rank's layers group by group during the last
+        micro-batch's backward pass (replicated gradients with HiMuon on CUDA; ``None`` switches it on whenever it
+        applies, ``False`` leaves the peer reads inside ``momentum_tile``).
         ``cpu_offload``: keep the optimizer's state tensors in pinned host memory between steps (see
         :class:`OptimizerStateOffload`; the reference's ``--cpu-offload``, ``train_fsdp.py:58,120``)."""
         self.model = model
         self.rank, self.world = _world()
         self.cpu_offload = bool(cpu_offload)
+        # gradient pre-fetch (decided in attach_optimizer): a stream of its own, so that weight copies never queue
+        # behind a barrier that waits for the slowest rank
+        self._grad_prefetch_wanted = grad_prefetch
+        self.grad_prefetch = False
+        self._grad_stream = None
+        self._sync_pass = True
+        self.graph_key_sync = False       # True: the synchronising micro-batch gets a CUDA graph of its own
+        self.grad_pulls = 0               # layer groups pulled so far (tests, diagnostics)
         self.gather_blocks = gather_blocks
         first = next(model.parameters())
         self.device, self.dtype = first.device, first.dtype
@@ -280,6 +296,7 @@ class ShardedEngine:
                 g += st.grad_full.shape[0] * m
             if st.gring is not None:
                 g += (st.gring.shape[0] + st.grad_shard.shape[0]) * m
+            g += sum(t.shape[0] for t in (getattr(st, "grad_stage", None) or []) if t is not None) * m
         return {"weights": w, "grads": g, "banks_total": total, "banks_padded": padded}
 
     # ------------------------------------------------------------------ optimizer hookup
@@ -296,6 +313,17 @@ class ShardedEngine:
             for st in self.state.values():
                 if hasattr(st.param, "_hm_grad_sources"):
                     del st.param._hm_grad_sources
+        want = self._grad_prefetch_wanted
+        if fused and self.world > 1 and self.weights_mode != "peer" and (want or want is None) and not self.grad_prefetch:
+            self.grad_prefetch = True
+            self.graph_key_sync = True
+            self._grad_stream = torch.cuda.Stream(self.device)
+            for st in self.state.values():
+                st.grad_peer = list(st.param._hm_grad_sources)       # peer r's replica of this rank's layers
+                st.grad_stage = [None if r == self.rank else torch.zeros_like(st.shard) for r in range(self.world)]
+                st.param._hm_grad_sources = [st.grad_peer[r] if r == self.rank else st.grad_stage[r]
+                                             for r in range(self.world)]
+            object.__setattr__(self.model, "_layer_hooks", self)
         if self.cpu_offload and self.cuda:
             self._offload = OptimizerStateOffload(optimizer)
         return optimizer
@@ -345,7 +373,8 @@ class ShardedEngine:
     # ---- layer-group fences (called by the decoder's layer loop)
     @property
     def uses_fences(self) -> bool:
-        return self.banks is not None and self.world > 1 and (self.weights_mode == "ring" or self.grads_mode == "sharded")
+        return self.banks is not None and self.world > 1 and (self.weights_mode == "ring" or self.grads_mode == "sharded"
+                                                              or self.grad_prefetch)
 
     def pre_layer(self, i: int, h, delta):
         """Before decoder layer ``i``: at the first layer of a group make the group's weights available and start
@@ -431,6 +460,34 @@ class ShardedEngine:
         else:                                          # group g's layers are done
             if self.grads_mode == "sharded":
                 self._reduce_group(g)
+            elif self.grad_prefetch and self._sync_pass:
+                self._pull_group_grads(g)
+
+    def _pull_group_grads(self, g: int):
+        """Last micro-batch of a step, layer group ``g`` differentiated: once every rank is past the group (a barrier
+        on the gradient stream's own channel), copy the peers' accumulated gradients of this rank's layer of the
+        group into the local staging buffers the optimizer reads.  Group 0 is the last one of a backward pass; the
+        compute stream joins the gradient stream there (inside the micro-batch's CUDA graph when one is captured)."""
+        self.grad_pulls += 1
+        main = torch.cuda.current_stream(self.device)
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(self._grad_stream):
+            self._grad_stream.wait_event(done)
+            self.heap.barrier(channel=1)
+            ops._count()
+            for j in range(1, self.world):
+                src = (self.rank + j) % self.world     # every rank's memory is read by one puller at a time
+                for st in self.state.values():
+                    if g * self.world + self.rank >= st.n_units:
+                        continue                       # this rank's slot of the group is a pad layer
+                    lo, hi = g * st.unit, (g + 1) * st.unit
+                    st.grad_stage[src][lo:hi].copy_(st.grad_peer[src][lo:hi], non_blocking=True)
+            if g == 0:
+                landed = torch.cuda.Event()
+                landed.record(self._grad_stream)
+        if g == 0:
+            main.wait_event(landed)
 
     def _prefetch(self, g: int):
         """Start copying layer group ``g`` into its staging slot.  The copies are ordered after everything enqueued on
@@ -501,7 +558,12 @@ class ShardedEngine:
 
     @contextmanager
     def no_sync(self):
-        yield
+        """Accumulation micro-steps: nothing is exchanged (the gradient pre-fetch belongs to the last micro-batch)."""
+        prev, self._sync_pass = self._sync_pass, False
+        try:
+            yield
+        finally:
+            self._sync_pass = prev
 
     def finish_backward(self):
         """Make every rank's accumulated gradients visible and reduce what the optimizer cannot reduce itself."""
@@ -557,6 +619,11 @@ class ShardedEngine:
             for st in self.state.values():
                 for slot in (st.ring or []):
                     slot.fill_(float("nan"))
+                for r, stage in enumerate(getattr(st, "grad_stage", None) or []):
+                    if stage is not None:              # pad slots keep zeros (momentum_tile skips them)
+                        for lu in range(self.n_groups):
+                            if lu * self.world + self.rank < st.n_units:
+                                stage[lu * st.unit:(lu + 1) * st.unit].fill_(float("nan"))
             bad = self.heap.check_canaries()
             if bad:
                 raise RuntimeError(f"ShardedEngine(debug): heap guard zones overwritten at offsets {bad}")

@@ -206,11 +206,14 @@ class SymmetricHeap:
         return self._host[offset:offset + nbytes].view(dtype).view(shape)
 
     # ------------------------------------------------------------------ collectives
-    def barrier(self):
+    def barrier(self, channel: int = 0):
+        """Stream-ordered barrier between the ranks' GPUs on the current stream.  ``channel=1`` is a second, independent
+        barrier (own flags and counters) for a side stream: calls on one channel must come in the same order on every
+        rank, calls on different channels may interleave differently from rank to rank."""
         if self.world == 1:
             return
         if self.cuda:
-            self.comm.barrier()
+            self.comm.barrier(channel)
         else:
             dist.barrier()
 

@@ -87,6 +87,9 @@ def build_arg_parser(mode: str) -> argparse.ArgumentParser:
                             "reduce-scatter onto the owner's shard-sized accumulator")
         p.add_argument("--peer-weights", dest="peer_weights", action="store_true",
                        help="same as --fsdp-weights peer")
+        p.add_argument("--no-grad-prefetch", dest="no_grad_prefetch", action="store_true",
+                       help="do not pull the peers' gradient replicas during the last micro-batch's backward pass "
+                            "(HiMuon then reads them over NVLink inside the optimizer step)")
     return p
 
 
@@ -396,7 +399,8 @@ def run_training(args, mode: str) -> dict:
         weights = "peer" if getattr(args, "peer_weights", False) else getattr(args, "fsdp_weights", "gathered")
         engine = ShardedEngine(model, use_banks=use_banks, cpu_offload=getattr(args, "cpu_offload", False),
                                weights=weights, grads=getattr(args, "fsdp_grads", "replicated"),
-                               nvls=bool(getattr(args, "nvls", False)))
+                               nvls=bool(getattr(args, "nvls", False)),
+                               grad_prefetch=False if getattr(args, "no_grad_prefetch", False) else None)
         banks = engine.banks
 
     tokens_per_step = args.batch_size * args.max_length * args.gradient_accumulation_steps * world_size

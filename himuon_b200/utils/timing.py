@@ -108,14 +108,22 @@ class PhaseTimer:
     def reset(self):
         self._events = {}
 
-    def summary(self, reduce_over_ranks: bool = True) -> dict:
+    def summary(self, reduce_over_ranks: bool = True, reduce: str = "max") -> dict:
+        """``reduce="max"`` gives each phase's longest time over the ranks; ``reduce="min"`` the shortest.  For a phase
+        that waits on the other ranks (a collective after the backward pass) the shortest time is the collective
+        itself, as seen by the rank that arrived last; the longest adds the time the first rank waited for the last."""
         if not self.enabled or not self._events:
             return {}
         torch.cuda.synchronize(self.device)
         out = {}
         for name, pairs in self._events.items():
             ms = sum(a.elapsed_time(b) for a, b in pairs)
-            out[name] = max_over_ranks(ms) if reduce_over_ranks else ms
+            if not reduce_over_ranks:
+                out[name] = ms
+            elif reduce == "min":
+                out[name] = -max_over_ranks(-ms)
+            else:
+                out[name] = max_over_ranks(ms)
         return out
 
 

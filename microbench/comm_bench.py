@@ -152,9 +152,11 @@ def main():
     out = torch.empty(shard_bytes // 2, device=device, dtype=torch.bfloat16)
     ms = _time(lambda: heap.comm.reduce_to(soff, out, 1.0 / world, 0.0), args.iters, args.warmup, None)
     report("reduce_scatter(reduce_to)", shard_bytes * world, ms, shard_bytes * (world - 1))
-    if heap.has_multicast:       # the switch sums the copies: this rank receives one copy's worth of bytes
+    if heap.has_multicast:
+        # the switch sums the copies: this rank receives one copy's worth of bytes, but every GPU still sends its
+        # copy of the other ranks' slices, so the outgoing direction carries what the plain reduce-scatter carries
         ms = _time(lambda: heap.comm.reduce_to(soff, out, 1.0 / world, 0.0, True), args.iters, args.warmup, None)
-        report("reduce_scatter_nvls", shard_bytes * world, ms, shard_bytes)
+        report("reduce_scatter_nvls", shard_bytes * world, ms, shard_bytes * (world - 1))
     if args.nccl:
         full = gathered.view(-1)
         ms = _time(lambda: dist.reduce_scatter_tensor(out, full), args.iters, args.warmup, None)

@@ -102,7 +102,8 @@ def scenario_train(mode, optimizer_name, device):
         # "fsdp-peer": no gathered copy; the GEMMs read the weights from the owner rank's shard over NVLink
         engine = ShardedEngine(model, use_banks=True, timeout_s=30.0, peer_weights=(mode == "fsdp-peer"),
                                weights=opts[0] if opts else None, grads=opts[1] if len(opts) > 1 else "replicated",
-                               nvls="nvls" in opts, debug="debug" in opts)
+                               nvls="nvls" in opts, debug="debug" in opts,
+                               grad_prefetch=False if "nopull" in opts else None)
         if mode == "fsdp-peer":
             assert any(st.gathered is None for st in engine.state.values()) or world == 1
         if opts and world > 1:
@@ -127,6 +128,10 @@ def scenario_train(mode, optimizer_name, device):
     opt = get_optimizer(optimizer_name, model, ns)
     if mode == "fsdp":
         engine.attach_optimizer(opt)
+        # HiMuon on replicated gradients: the peers' replicas are pulled during the last micro-batch's backward pass
+        pulls = (world > 1 and optimizer_name == "himuon" and engine.grads_mode == "replicated" and not engine.nvls
+                 and engine.weights_mode != "peer" and "nopull" not in opts)
+        assert engine.grad_prefetch == pulls, (engine.grad_prefetch, pulls)
     trainer = Trainer(model, opt, None, engine, grad_acc=2, device=device, graph_microbatch="graph" in opts,
                       graph_warmup_steps=1)
     trainer.zero_set_to_none = False
@@ -139,6 +144,9 @@ def scenario_train(mode, optimizer_name, device):
     sd = engine.full_state_dict() if mode == "fsdp" else {k: v.detach().cpu() for k, v in model.state_dict().items()}
     if mode == "ddp" and engine.overlap:
         assert engine.overlapped_launches >= engine.n_buckets, engine.overlapped_launches
+    if mode == "fsdp" and engine.grad_prefetch:
+        assert engine.grad_pulls >= engine.n_groups, engine.grad_pulls
+        assert engine.bank_bytes()["grads"] > 0
     if "graph" in opts:
         assert {k[0] for k in trainer._mb_graphs} == {True, False}, "the micro-batch graphs were not captured"
     if rank == 0:
