@@ -65,7 +65,7 @@ from .symm import SymmetricHeap, _world
 
 class _BankState:
     __slots__ = ("spec", "unit", "n_units", "n_local", "shard", "shard_off", "grad_full", "grad_off", "gathered",
-                 "param", "sinks", "pair_sinks", "peer_shards", "ring", "gring", "gring_off", "grad_shard")
+                 "param", "sinks", "pair_sinks", "peer_shards", "ring", "gring", "gring_off", "grad_shard", "grad_peer", "grad_stage")
 
 
 class ShardedEngine:
@@ -171,7 +171,7 @@ class ShardedEngine:
                 owner, loc = self._place(st, s)
                 if owner == self.rank:
                     st.shard[loc].copy_(full.data[s])
-            st.grad_full = st.gring = st.grad_shard = None
+            st.grad_full = st.gring = st.grad_shard = st.grad_peer = st.grad_stage = None
             st.grad_off = st.gring_off = 0
             if grads == "replicated":
                 st.grad_full, st.grad_off = self.heap.alloc((n_phys, H, W), self.dtype)
@@ -296,7 +296,7 @@ class ShardedEngine:
                 g += st.grad_full.shape[0] * m
             if st.gring is not None:
                 g += (st.gring.shape[0] + st.grad_shard.shape[0]) * m
-            g += sum(t.shape[0] for t in (getattr(st, "grad_stage", None) or []) if t is not None) * m
+            g += sum(t.shape[0] for t in (st.grad_stage or []) if t is not None) * m
         return {"weights": w, "grads": g, "banks_total": total, "banks_padded": padded}
 
     # ------------------------------------------------------------------ optimizer hookup
@@ -619,7 +619,7 @@ class ShardedEngine:
             for st in self.state.values():
                 for slot in (st.ring or []):
                     slot.fill_(float("nan"))
-                for r, stage in enumerate(getattr(st, "grad_stage", None) or []):
+                for stage in (st.grad_stage or []):
                     if stage is not None:              # pad slots keep zeros (momentum_tile skips them)
                         for lu in range(self.n_groups):
                             if lu * self.world + self.rank < st.n_units:
