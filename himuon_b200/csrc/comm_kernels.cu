@@ -3,8 +3,8 @@
 //
 //   peer_barrier     : stream-ordered barrier between the ranks' GPUs (one tiny launch)
 //   allreduce_symm   : one-launch all-reduce with the average / cast fused: two-shot (reduce-scatter by
-//                      peer loads, all-gather by peer stores) for bandwidth-bound regions, one-shot
-//                      (every rank reads everything, no peer stores) for regions up to 256 KiB;
+//                      peer loads, all-gather by peer stores); a one-shot variant (every rank reads
+//                      everything, no peer stores) exists for regions up to 2 MiB and is selected by hand;
 //                      replaces the DDP reducer's bucketed NCCL all-reduce (reference:
 //                      train_ddp.py:90, implicit)
 //   reduce_replicas  : out = beta * out + scale * sum_r replica_r, the owner-side half of a
@@ -180,11 +180,13 @@ void allreduce_symm(const CommPeers& peers, const CommBufs& bufs, long long n_el
   const int vec = is_fp32 ? 4 : 8;
   if (n_elems % (static_cast<long long>(vec) * peers.world))
     throw std::runtime_error("himuon allreduce: element count must be a multiple of (16 bytes * world size)");
-  // algo 0: pick by size (one-shot up to 256 KiB), 1: one-shot, 2: two-shot
+  // algo 0 and 2: two-shot, 1: one-shot.  The one-shot kernel is never picked automatically: with its two handshakes
+  // it measured no faster than the two-shot kernel even at 64 KiB (0.035 vs 0.032 ms on 2 ranks, 0.053 vs 0.039 ms
+  // on 4), because every rank then reads `world` copies where the two-shot kernel reads and writes one.
   const long long bytes = n_elems * (is_fp32 ? 4 : 2);
   if (algo == 1 && bytes > kOneShotMaxBytes)
     throw std::runtime_error("himuon allreduce: region too large for the one-shot kernel");
-  if (algo == 1 || (algo == 0 && bytes <= (256 << 10))) {
+  if (algo == 1) {
     const long long n_vec = n_elems / vec;
     long long blocks = (n_vec + 512LL * kOneShotVecPerThread - 1) / (512LL * kOneShotVecPerThread);
     if (blocks < 1) blocks = 1;                       // by the size limit above, blocks <= 64 < kCommMaxBlocks

@@ -7,7 +7,7 @@ synchronising micro-step the reduction overlaps the backward pass the way the DD
 (``train_ddp.py:90``): the decoder layers' matrices are laid out layer by layer, a bucket is a run of consecutive
 layers, and as soon as the backward pass has left a bucket's first layer its all-reduce starts on a side stream with
 a small grid, beside the remaining backward GEMMs.  What is left when backward ends (embeddings, norm weights, whose
-gradients are folded in at the very end) is reduced by one more launch; regions up to 256 KiB take the one-shot kernel.
+gradients are folded in at the very end) is reduced by one more launch.
 Replaces ``torch.nn.parallel.DistributedDataParallel`` and its bucketed NCCL all-reduce.
 """
 
@@ -105,8 +105,7 @@ class DataParallelEngine:
         object.__setattr__(model, "_layer_hooks", self if self.overlap else None)
 
     def _region_algo(self, flat) -> int:
-        """Through the switch when the heap has a multicast mapping, except for regions small enough for the
-        latency-bound one-shot kernel."""
+        """Through the switch when the heap has a multicast mapping, except for small, latency-bound regions."""
         if self._algo == 3 and flat.numel() * flat.element_size() > (256 << 10):
             return 3
         return 0

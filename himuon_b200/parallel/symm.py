@@ -218,9 +218,9 @@ class SymmetricHeap:
             dist.barrier()
 
     def allreduce_(self, tensor: torch.Tensor, offset: int, scale: float, max_blocks: int = 0, algo: int = 0):
-        """In-place sum over ranks of the region ``tensor`` (at ``offset``) times ``scale``.  ``algo``: 0 picks the
-        one-shot kernel up to 256 KiB and the two-shot kernel above, 1 / 2 force one of them, 3 reduces and broadcasts
-        through the NVLink switch (needs a multicast heap); ``max_blocks`` caps the two-shot grid (a small grid
+        """In-place sum over ranks of the region ``tensor`` (at ``offset``) times ``scale``.  ``algo``: 0 and 2 run the
+        two-shot kernel, 1 the one-shot kernel (regions up to 2 MiB; measured no faster than two-shot at any size, so
+        never chosen automatically), 3 reduces and broadcasts through the NVLink switch (needs a multicast heap); ``max_blocks`` caps the two-shot grid (a small grid
         leaves the SMs to a compute stream that runs beside it)."""
         if self.world == 1:
             if scale != 1.0:

@@ -6,7 +6,7 @@
 Times, with CUDA events on the launching stream after a barrier (maximum over ranks, median of ``--iters`` launches
 after ``--warmup``), the kernels the engines use for their bulk traffic:
 
-* ``allreduce`` - the fused all-reduce (one-shot up to 256 KiB, two-shot above) on region sizes from 64 KiB to
+* ``allreduce`` - the fused two-shot all-reduce on region sizes from 64 KiB to
   ``--max-mb`` and on the gradient sizes of Qwen3-0.6B (data-parallel configuration);
 * ``allreduce_16blk`` - the same with the 16-block grid the data-parallel engine uses beside the backward GEMMs;
 * ``bank_gather`` - ``multi_copy`` pulling every peer's bank shard (the once-per-step re-gather of the gathered mode);
@@ -108,8 +108,8 @@ def main():
             ms = _time(lambda: heap.allreduce_(buf[:n], off, 1.0 / world, max_blocks=16), args.iters, args.warmup, fl)
             report("allreduce_16blk", n * 2, ms, ar_factor * n * 2)
         if nbytes <= (1 << 20):
-            ms = _time(lambda: heap.allreduce_(buf[:n], off, 1.0 / world, algo=2), args.iters, args.warmup, fl)
-            report("allreduce_twoshot_forced", n * 2, ms, ar_factor * n * 2)
+            ms = _time(lambda: heap.allreduce_(buf[:n], off, 1.0 / world, algo=1), args.iters, args.warmup, fl)
+            report("allreduce_oneshot", n * 2, ms, ar_factor * n * 2)
         if heap.has_multicast and nbytes >= (1 << 20):
             ms = _time(lambda: heap.allreduce_(buf[:n], off, 1.0 / world, algo=3), args.iters, args.warmup, fl)
             report("allreduce_nvls", n * 2, ms, ar_factor * n * 2)
