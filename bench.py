@@ -55,9 +55,9 @@ def parse():
                    help="bank working copy: full gathered copy (default), two-slot staging ring, or peer reads")
     p.add_argument("--fsdp-grads", type=str, default="replicated", choices=["replicated", "sharded"],
                    help="bank gradient accumulation: full buffer per rank (default) or per-group reduce-scatter")
-    p.add_argument("--no-grad-prefetch", action="store_true",
-                   help="sharded engine: leave the peers' gradient replicas to momentum_tile's peer loads instead of "
-                        "pulling them with the copy engines during the last micro-batch's backward pass")
+    p.add_argument("--grad-prefetch", action="store_true",
+                   help="sharded engine: pull the peers' gradient replicas with the copy engines during the last "
+                        "micro-batch's backward pass instead of leaving them to momentum_tile's peer loads")
     p.add_argument("--nvls", action="store_true",
                    help="gradient reductions through the NVLink switch (multimem) instead of peer loads")
     p.add_argument("--ddp-serial", action="store_true",
@@ -155,7 +155,7 @@ def run_ours(args):
         weights = "peer" if args.peer_weights else args.fsdp_weights
         engine = ShardedEngine(model, use_banks=args.optimizer in ("himuon", "muon-fsdp", "adamw"), weights=weights,
                                grads=args.fsdp_grads, nvls=args.nvls,
-                               grad_prefetch=False if args.no_grad_prefetch else None)
+                               grad_prefetch=args.grad_prefetch)
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
         engine = DataParallelEngine(model, nvls=args.nvls, overlap=not args.ddp_serial, comm_blocks=args.ddp_comm_blocks)

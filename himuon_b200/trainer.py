@@ -87,9 +87,9 @@ def build_arg_parser(mode: str) -> argparse.ArgumentParser:
                             "reduce-scatter onto the owner's shard-sized accumulator")
         p.add_argument("--peer-weights", dest="peer_weights", action="store_true",
                        help="same as --fsdp-weights peer")
-        p.add_argument("--no-grad-prefetch", dest="no_grad_prefetch", action="store_true",
-                       help="do not pull the peers' gradient replicas during the last micro-batch's backward pass "
-                            "(HiMuon then reads them over NVLink inside the optimizer step)")
+        p.add_argument("--grad-prefetch", dest="grad_prefetch", action="store_true",
+                       help="pull the peers' gradient replicas with the copy engines during the last micro-batch's "
+                            "backward pass (HiMuon otherwise reads them over NVLink inside the optimizer step)")
     return p
 
 
@@ -400,7 +400,7 @@ def run_training(args, mode: str) -> dict:
         engine = ShardedEngine(model, use_banks=use_banks, cpu_offload=getattr(args, "cpu_offload", False),
                                weights=weights, grads=getattr(args, "fsdp_grads", "replicated"),
                                nvls=bool(getattr(args, "nvls", False)),
-                               grad_prefetch=False if getattr(args, "no_grad_prefetch", False) else None)
+                               grad_prefetch=bool(getattr(args, "grad_prefetch", False)))
         banks = engine.banks
 
     tokens_per_step = args.batch_size * args.max_length * args.gradient_accumulation_steps * world_size

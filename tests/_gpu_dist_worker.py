@@ -103,7 +103,7 @@ def scenario_train(mode, optimizer_name, device):
         engine = ShardedEngine(model, use_banks=True, timeout_s=30.0, peer_weights=(mode == "fsdp-peer"),
                                weights=opts[0] if opts else None, grads=opts[1] if len(opts) > 1 else "replicated",
                                nvls="nvls" in opts, debug="debug" in opts,
-                               grad_prefetch=False if "nopull" in opts else None)
+                               grad_prefetch="pull" in opts)
         if mode == "fsdp-peer":
             assert any(st.gathered is None for st in engine.state.values()) or world == 1
         if opts and world > 1:
@@ -130,7 +130,7 @@ def scenario_train(mode, optimizer_name, device):
         engine.attach_optimizer(opt)
         # HiMuon on replicated gradients: the peers' replicas are pulled during the last micro-batch's backward pass
         pulls = (world > 1 and optimizer_name == "himuon" and engine.grads_mode == "replicated" and not engine.nvls
-                 and engine.weights_mode != "peer" and "nopull" not in opts)
+                 and engine.weights_mode != "peer" and "pull" in opts)
         assert engine.grad_prefetch == pulls, (engine.grad_prefetch, pulls)
     trainer = Trainer(model, opt, None, engine, grad_acc=2, device=device, graph_microbatch="graph" in opts,
                       graph_warmup_steps=1)

@@ -54,8 +54,8 @@ def test_peer_memory_collectives():
 @needs2
 @pytest.mark.parametrize("mode,opt", [("fsdp", "himuon"), ("ddp", "himuon"), ("fsdp", "muon-fsdp"), ("fsdp", "adamw"),
                                       ("fsdp-peer", "himuon"), ("fsdp:ring:replicated", "himuon"),
-                                      ("fsdp:gathered:replicated:graph", "himuon"), ("fsdp:gathered:replicated:nopull", "himuon"),
-                                      ("fsdp:gathered:replicated:debug:ckpt", "himuon"),
+                                      ("fsdp:gathered:replicated:graph:pull", "himuon"), ("fsdp:ring:replicated:pull", "himuon"),
+                                      ("fsdp:gathered:replicated:debug:ckpt:pull", "himuon"),
                                       ("fsdp:ring:replicated:graph", "himuon"), ("fsdp:gathered:sharded", "himuon"),
                                       ("fsdp:ring:sharded:graph:ckpt:debug", "himuon"), ("fsdp:ring:sharded", "adamw"),
                                       ("fsdp:ring:sharded", "muon-fsdp"), ("ddp:overlap:graph", "himuon"),
