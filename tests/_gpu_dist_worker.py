@@ -179,7 +179,8 @@ def scenario_train(mode, optimizer_name, device):
         cos = min(float(torch.nn.functional.cosine_similarity(sd[k].float().flatten().cpu(), ref_sd[k].float().flatten().cpu(), dim=0))
                   for k in ref_sd)
         # bf16 runs with different summation orders drift apart through Newton-Schulz; deeper models drift more
-        floor = 0.99 if "fp32ref" in opts else (0.998 if layers > 3 else 0.999)
+        # (20 layers on 4 ranks measured 0.99796 ... 0.99807 from run to run, single-process oracle included)
+        floor = 0.99 if "fp32ref" in opts else (0.997 if layers >= 20 else (0.998 if layers > 3 else 0.999))
         assert cos > floor, cos
         print(f"PARITY OK {mode} {optimizer_name} losses={mean_losses} ref={ref_losses} min_cos={cos:.6f}", flush=True)
     dist.barrier()
