@@ -167,7 +167,7 @@ struct CommBufs { void* ptr[kMaxSrc]; };
 struct CopySeg { const void* src; void* dst; long long bytes; long long unit_begin; };
 // epoch_local: int[2*kCommMaxBlocks] private to this rank, zero-initialised, advanced by the kernels.
 void peer_barrier(const CommPeers& peers, int* epoch_local, cudaStream_t s, int channel = 0);
-// algo 0: by size (one-shot up to 256 KiB, two-shot above), 1: one-shot (regions up to 2 MiB), 2: two-shot.
+// algo 0 and 2: two-shot (every size), 1: one-shot (regions up to 2 MiB; never chosen automatically).
 void allreduce_symm(const CommPeers& peers, const CommBufs& bufs, long long n_elems, int is_fp32, float scale,
                     int* epoch_local, int max_blocks, cudaStream_t s, int algo = 0);
 // NVLS variants: `mc_region` is the multicast address of the region (all ranks' copies behind one address, vmm.cpp).
