@@ -31,9 +31,15 @@ def methods(tiles):
 
 
 def native_fp8_available() -> bool:
-    if not have_cuda() or not hasattr(torch, "_scaled_mm"):
+    """True when a small fp8-e4m3 product actually runs on this machine (GPU with fp8 tensor cores and a PyTorch that
+    exposes the scaled matmul)."""
+    if not have_cuda() or not hasattr(torch, "_scaled_mm") or torch.cuda.get_device_capability() < (8, 9):
         return False
-    return torch.cuda.get_device_capability() >= (8, 9)
+    try:
+        x = torch.randn(32, 32, device="cuda")
+        return bool(torch.isfinite(am.fp8_matmul(x, x)).all())
+    except Exception:
+        return False
 
 
 def default_precisions():
