@@ -3,7 +3,7 @@
 The reference's ``microbench/assoc_mem.py:1-831`` studies how much of a Zipf-weighted set of key -> value
 associations one optimizer step recovers when the gradient is replaced by its (tile-local) orthogonalisation, at
 several arithmetic precisions.  This module provides the same building blocks: the quintic Newton-Schulz operator
-at a chosen precision (fp64 / fp32 / bf16 / simulated fp8-e4m3 / native fp8-e4m3 matmuls on the GPU), matrix tiling
+at a chosen precision (fp64 / fp32 / bf16 products / fp8-e4m3 products, simulated or on the GPU's fp8 tensor cores), matrix tiling
 with square or rectangular tiles, the HiMuon operator, the synthetic problem in both of the reference's forms (the
 compact ``zipf_problem`` and the ``sample_problem`` / ``build_gradient`` pair with population / minibatch and
 approximate / exact-softmax gradients), and the recovery metrics (per item, by frequency rank, top-k curves,
@@ -27,40 +27,65 @@ NS_PRECISIONS = PRECISIONS + ("fp8e4m3_native",)       # the last one needs a CU
 RANK_FRACTIONS = (0.0, 0.01, 0.05, 0.10, 0.25, 0.50, 1.0)
 
 
-def _fp8_round(x: torch.Tensor) -> torch.Tensor:
-    """Round-trip through float8_e4m3 with a per-tensor scale (simulates an fp8 matmul operand)."""
-    amax = x.abs().max().clamp(min=1e-12)
+def _precision_ops(ns_precision: str):
+    """``(store, matmul)`` of a precision: ``store`` is applied to the input, to the normalised iterate and to every
+    intermediate of the iteration (what a buffer of that precision would hold), ``matmul`` forms the products.
+
+    * ``fp64_ref`` / ``fp32``: everything in that type;
+    * ``bf16``: fp32 buffers, products of operands rounded to bf16 with fp32 accumulation (tensor-core semantics);
+    * ``fp8e4m3_native``: fp32 buffers, products on the GPU's fp8 tensor cores (operands quantised per matrix);
+    * ``fp8e4m3_sim``: the same arithmetic without fp8 hardware: both operands of every product are rounded through
+      float8-e4m3 under a per-matrix scale and multiplied in fp32.  (The reference's simulated mode instead stores
+      every *buffer* in fp8, which it does not use for its table; here the simulated mode tracks the native one, so
+      that a machine without fp8 tensor cores reproduces the native column.)
+
+    fp64 / fp32 / bf16 / native fp8 have the rounding points of the reference's engine
+    (``microbench/assoc_mem.py:345-397``), so the operator gaps compare with its table."""
+    if ns_precision == "fp64_ref":
+        return (lambda t: t.double()), torch.matmul
+    if ns_precision == "fp32":
+        return (lambda t: t.float()), torch.matmul
+    if ns_precision == "bf16":
+        return (lambda t: t.float()), (lambda l, r: (l.to(torch.bfloat16) @ r.to(torch.bfloat16)).float())
+    if ns_precision == "fp8e4m3_sim":
+        return (lambda t: t.float()), (lambda l, r: _fp8_round_each(l) @ _fp8_round_each(r))
+    if ns_precision == "fp8e4m3_native":
+        return (lambda t: t.float()), _fp8_matmul_batched
+    raise ValueError(f"unknown ns_precision {ns_precision!r}; choose from {NS_PRECISIONS}")
+
+
+def _fp8_round_each(x: torch.Tensor) -> torch.Tensor:
+    """Round-trip through float8-e4m3 with one scale per matrix of a (possibly batched) tensor."""
+    x = x.float()
+    amax = x.abs().amax(dim=(-2, -1), keepdim=True).clamp(min=1e-12)
     scale = 448.0 / amax
-    return (x * scale).to(torch.float8_e4m3fn).to(x.dtype) / scale
+    return (x * scale).to(torch.float8_e4m3fn).float() / scale
+
+
+def _fp8_matmul_batched(left: torch.Tensor, right: torch.Tensor) -> torch.Tensor:
+    if left.ndim == 2:
+        return fp8_matmul(left, right)
+    return torch.stack([fp8_matmul(a, b) for a, b in zip(left.reshape(-1, *left.shape[-2:]), right.reshape(-1, *right.shape[-2:]))]
+                       ).reshape(*left.shape[:-1], right.shape[-1])
 
 
 def quintic_ns_operator(g: torch.Tensor, steps: int = 5, ns_precision: str = "fp32") -> torch.Tensor:
-    """Newton-Schulz polar-factor approximation of the last two dims of ``g`` at the requested precision."""
-    if ns_precision == "fp64_ref":
-        return ref.newton_schulz(g.double(), steps, compute_dtype=torch.float64).to(g.dtype)
-    if ns_precision == "fp32":
-        return ref.newton_schulz(g.float(), steps, compute_dtype=torch.float32).to(g.dtype)
-    if ns_precision == "bf16":
-        return ref.newton_schulz(g.float(), steps, compute_dtype=torch.bfloat16).to(g.dtype)
-    if ns_precision == "fp8e4m3_native":
-        return _ns_fp8_native(g, steps)
-    if ns_precision == "fp8e4m3_sim":
-        a, b, c = ref.NS_COEFFS
-        X = g.float()
-        tall = X.size(-2) > X.size(-1)
-        if tall:
-            X = X.transpose(-2, -1)
-        X = X / (X.norm(dim=(-2, -1), keepdim=True) + 1e-7)
-        for _ in range(steps):
-            Xq = _fp8_round(X)
-            A = Xq @ Xq.transpose(-2, -1)
-            Aq = _fp8_round(A)
-            Bm = b * A + c * (Aq @ Aq)
-            X = a * X + _fp8_round(Bm) @ Xq
-        if tall:
-            X = X.transpose(-2, -1)
-        return X.to(g.dtype)
-    raise ValueError(f"unknown ns_precision {ns_precision!r}; choose from {NS_PRECISIONS}")
+    """Newton-Schulz polar-factor approximation of the last two dims of ``g`` (2-D or batched) with every buffer and
+    product held at the requested precision; returns ``g``'s dtype."""
+    store, mm = _precision_ops(ns_precision)
+    a, b, c = ref.NS_COEFFS
+    X = store(g)
+    tall = X.size(-2) > X.size(-1)
+    if tall:
+        X = X.transpose(-2, -1)
+    X = store(X / (X.norm(dim=(-2, -1), keepdim=True) + 1e-7))
+    for _ in range(steps):
+        A = store(mm(X, X.transpose(-2, -1)))
+        Bm = store(b * A + c * mm(A, A))
+        X = store(a * X + mm(Bm, X))
+    if tall:
+        X = X.transpose(-2, -1)
+    return X.to(g.dtype)
 
 
 def fp8_matmul(left: torch.Tensor, right: torch.Tensor) -> torch.Tensor:
@@ -77,23 +102,6 @@ def fp8_matmul(left: torch.Tensor, right: torch.Tensor) -> torch.Tensor:
     l8 = (lf / ls).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).contiguous()
     r8 = (rf / rs).clamp(-448.0, 448.0).t().contiguous().to(torch.float8_e4m3fn).t()      # column-major, as the op wants
     return torch._scaled_mm(l8, r8, scale_a=ls, scale_b=rs, out_dtype=torch.float32)
-
-
-def _ns_fp8_native(g: torch.Tensor, steps: int) -> torch.Tensor:
-    """The quintic iteration with every product on fp8 tensor cores; batched input is looped (the op is 2-D)."""
-    if g.ndim > 2:
-        return torch.stack([_ns_fp8_native(m, steps) for m in g.reshape(-1, *g.shape[-2:])]).reshape(g.shape)
-    a, b, c = ref.NS_COEFFS
-    X = g.float()
-    tall = X.size(0) > X.size(1)
-    if tall:
-        X = X.t()
-    X = X / (X.norm() + 1e-7)
-    for _ in range(steps):
-        A = fp8_matmul(X, X.t())
-        Bm = b * A + c * fp8_matmul(A, A)
-        X = a * X + fp8_matmul(Bm, X)
-    return (X.t() if tall else X).to(g.dtype)
 
 
 def _tile_hw(tile) -> tuple[int, int]:
