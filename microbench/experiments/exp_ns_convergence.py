@@ -23,7 +23,7 @@ import torch
 
 from himuon_b200.optimizers import HiMuon
 
-from ..bench_utils import batched_polar_cosine, default_device, experiment_main, mean_std, polar_factor
+from ..bench_utils import default_device, experiment_main, mean_std, polar_factor
 from ..plot_style import line_chart, text_table, write_text
 
 NAME = "ns_convergence"

@@ -57,8 +57,6 @@ def test_cli_trains_and_saves_hf_checkpoint(tmp_path, script):
     firing, the stop line, and an un-banked Hugging Face checkpoint (reference: test_himuon_fsdp_smoke.py)."""
     import re
 
-    import torch
-
     sched = '[{"step": 0, "tile_size": 1000000000}, {"step": 2, "tile_size": 32}]'
     r = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
