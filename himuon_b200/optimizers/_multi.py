@@ -6,6 +6,8 @@ import struct
 
 import torch
 
+from . import _tablecheck
+
 
 class PinnedHyper:
     """Per-group hyper-parameter rows (lr, wd, betas, eps) staged through pinned host memory.
@@ -64,11 +66,16 @@ class AdamTable:
         taken with these moments (a loaded state dict), so bias correction continues instead of restarting."""
         by: dict[tuple, dict] = {}
         for par, g, m, v, gi in items:
-            rec = by.setdefault((par.dtype, g.dtype), {"tab": bytearray(), "n": 0, "units": 0})
+            rec = by.setdefault((par.dtype, g.dtype), {"tab": bytearray(), "n": 0, "units": 0, "live": []})
             rec["tab"] += struct.pack("<4Qqq2i", par.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(),
                                       par.numel(), rec["units"], gi, 0)
             rec["n"] += 1
             rec["units"] += (par.numel() + 4095) // 4096
+            rec["live"] += [par, g, m, v]
+        if _tablecheck.enabled():
+            for (pdt, gdt), r in by.items():
+                _tablecheck.check_adam_table(bytes(r["tab"]), r["n"], r["units"], n_groups, pdt.itemsize, gdt.itemsize,
+                                             _tablecheck.Extents(r["live"]))
         self.recs = [
             {"tab": torch.frombuffer(r["tab"], dtype=torch.uint8).to(device), "n": r["n"], "units": r["units"],
              "param_fp32": k[0] == torch.float32, "state_fp32": k[1] == torch.float32}

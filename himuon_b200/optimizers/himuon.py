@@ -32,6 +32,7 @@ import torch
 from torch.optim import Optimizer
 
 from ..ops import ns as ns_ops
+from . import _tablecheck
 from ._multi import PinnedHyper
 from ..ops import reference as ref
 
@@ -451,6 +452,18 @@ class HiMuon(Optimizer):
                     app_tab += struct.pack("<Qq6ifi", par.data_ptr(), m.tile_base, m.h, m.w, m.R, m.C, unit,
                                            m.group_idx, scale, par.stride(0))
                     unit += e.momentum_tile_units(m.R, m.C, th)
+                if _tablecheck.enabled():
+                    ext_ranges = _tablecheck.Extents()
+                    for m in sub:
+                        for t in (getattr(m.param, "_hm_grad_sources", None) or [_local(m.param.grad)]):
+                            ext_ranges.add(t)
+                        ext_ranges.add(self._momentum_buffer(m.param))
+                        ext_ranges.add(_local(m.param.data))
+                    units_of = lambda R, C: e.momentum_tile_units(R, C, th)   # noqa: E731
+                    _tablecheck.check_momentum_table(bytes(mom_tab), len(sub), th, tw, buf.shape[0], units_of, unit, n_src,
+                                                     4 if gdtype == torch.float32 else 2, ext_ranges)
+                    _tablecheck.check_apply_table(bytes(app_tab), len(sub), th, tw, buf.shape[0], units_of, unit, n_groups,
+                                                  4 if pdtype == torch.float32 else 2, ext_ranges)
                 launches.append({
                     "mom_tab": torch.frombuffer(mom_tab, dtype=torch.uint8).to(device),
                     "app_tab": torch.frombuffer(app_tab, dtype=torch.uint8).to(device),
@@ -478,11 +491,16 @@ class HiMuon(Optimizer):
                     st["moment1"] = torch.zeros_like(g)
                     st["moment2"] = torch.zeros_like(g)
                 par = _local(p.data)
-                rec = adam.setdefault((par.dtype, g.dtype), {"tab": bytearray(), "n": 0, "units": 0})
+                rec = adam.setdefault((par.dtype, g.dtype), {"tab": bytearray(), "n": 0, "units": 0, "live": []})
                 rec["tab"] += struct.pack("<4Qqq2i", par.data_ptr(), g.data_ptr(), st["moment1"].data_ptr(),
                                           st["moment2"].data_ptr(), par.numel(), rec["units"], gi, 0)
                 rec["n"] += 1
                 rec["units"] += (par.numel() + 4095) // 4096
+                rec["live"] += [par, g, st["moment1"], st["moment2"]]
+        if _tablecheck.enabled():
+            for (pdt, gdt), r in adam.items():
+                _tablecheck.check_adam_table(bytes(r["tab"]), r["n"], r["units"], n_groups, pdt.itemsize, gdt.itemsize,
+                                             _tablecheck.Extents(r["live"]))
         self._adam_exec = [
             {"tab": torch.frombuffer(r["tab"], dtype=torch.uint8).to(device), "n": r["n"], "units": r["units"],
              "param_fp32": k[0] == torch.float32, "state_fp32": k[1] == torch.float32}

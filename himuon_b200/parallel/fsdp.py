@@ -78,7 +78,7 @@ class ShardedEngine:
         read through it (``multimem.ld_reduce``: the switch sums the ranks' copies, the owner receives one copy's worth
         of bytes instead of ``world - 1``) and the replicated parameters' all-reduce goes through the switch too.
         ``debug``: race / overrun checks for development - guard zones after every heap region (``heap.check_canaries()``,
-        verified in ``zero_grad``), and staging slots and group gradient buffers are filled with NaN whenever their
+        verified in ``zero_grad``), host-side bounds checks of the optimizers' device tables, and staging slots and group gradient buffers are filled with NaN whenever their
         contents become stale, so a kernel that reads a slot before its copy has landed poisons the loss visibly.
         ``grad_prefetch``: pull the peers' gradient replicas of this rank's layers group by group during the last
         micro-batch's backward pass (replicated gradients with HiMuon on CUDA; off by default, which leaves the peer
@@ -137,6 +137,8 @@ class ShardedEngine:
         self.debug = bool(debug)
         if self.debug:
             need += 64 * SymmetricHeap.CANARY_BYTES + 64 * 1024
+            from ..optimizers import _tablecheck
+            _tablecheck.enable(True)              # the optimizers validate their device tables against the live tensors
         self.heap = SymmetricHeap(need, self.device, timeout_s, multicast=nvls, canaries=self.debug)
         self.nvls = self.heap.has_multicast
 

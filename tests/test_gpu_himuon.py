@@ -51,6 +51,28 @@ def test_smoke_finite_and_changed(dtype, tile):
         assert torch.isfinite(p).all() and not torch.equal(p, b)
 
 
+def test_device_tables_pass_the_host_side_bounds_check():
+    """With the table checks on, HiMuon (tiled, padded and whole-matrix parameters plus an AdamW-fallback group) and the
+    AdamW class build their device tables and step; the checks walk every entry against the live tensors."""
+    from himuon_b200.optimizers import AdamW, HiMuon, _tablecheck
+
+    _tablecheck.enable(True)
+    try:
+        model = make_linear_model([(512, 512), (768, 520), (64, 64), (256, 1024)], torch.bfloat16, "cuda")
+        bias = torch.nn.Parameter(torch.zeros(96, device="cuda", dtype=torch.bfloat16))
+        bias.grad = torch.ones_like(bias)
+        opt = HiMuon([{"params": list(model.parameters())}, {"params": [bias], "use_muon": False, "lr": 1e-3}],
+                     tile_size=(128, 256), cuda_graph=False)
+        seed_grads(model, 0)
+        opt.step()
+        adam = AdamW(list(model.parameters()) + [bias], lr=1e-3)
+        adam.step()
+        torch.cuda.synchronize()
+        assert all(torch.isfinite(p).all() for p in model.parameters())
+    finally:
+        _tablecheck.enable(False)
+
+
 def _run(b_hw=None, cuda_graph=False, steps=5, dtype=torch.bfloat16):
     from himuon_b200.optimizers import HiMuon
 
