@@ -59,6 +59,9 @@ def parse():
                         "micro-batch's backward pass instead of leaving them to momentum_tile's peer loads")
     p.add_argument("--nvls", action="store_true",
                    help="gradient reductions through the NVLink switch (multimem) instead of peer loads")
+    p.add_argument("--ddp-overlap", action="store_true",
+                   help="data-parallel engine: per-bucket all-reduces on a side stream beside the backward pass instead of "
+                        "one full-grid all-reduce after it (the default)")
     p.add_argument("--ddp-serial", action="store_true",
                    help="data-parallel engine: one all-reduce after backward instead of per-bucket all-reduces beside it")
     p.add_argument("--ddp-comm-blocks", type=int, default=16, help="grid cap of the overlapped bucket all-reduces")
@@ -157,7 +160,7 @@ def run_ours(args):
                                grad_prefetch=args.grad_prefetch)
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
-        engine = DataParallelEngine(model, nvls=args.nvls, overlap=not args.ddp_serial, comm_blocks=args.ddp_comm_blocks)
+        engine = DataParallelEngine(model, nvls=args.nvls, overlap=args.ddp_overlap and not args.ddp_serial, comm_blocks=args.ddp_comm_blocks)
     ns = argparse.Namespace(lr=LR if args.optimizer != "adamw" else 1e-3, weight_decay=WD, tile_size=args.tile, cuda_graph=True,
                             cuda_graph_warmup=1)
     optimizer = get_optimizer(args.optimizer, model, ns)
@@ -232,7 +235,7 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
             "config": {"model": args.model, "global_batch": args.micro_batch * args.grad_acc * world,
                        "seq_len": args.seq_len, "micro_batch_per_gpu": args.micro_batch, "grad_acc": args.grad_acc,
-                       "parallelism": (f"fsdp-banks{world}" + (f" weights={engine.weights_mode} grads={engine.grads_mode}" + (" nvls" if engine.nvls else "") + (" grad-prefetch" if engine.grad_prefetch else "") if world > 1 else "")) if args.engine == "fsdp" else f"dp{world}" + ("" if world == 1 else (" serial all-reduce" if args.ddp_serial else " overlapped bucket all-reduce")),
+                       "parallelism": (f"fsdp-banks{world}" + (f" weights={engine.weights_mode} grads={engine.grads_mode}" + (" nvls" if engine.nvls else "") + (" grad-prefetch" if engine.grad_prefetch else "") if world > 1 else "")) if args.engine == "fsdp" else f"dp{world}" + ("" if world == 1 else (" overlapped bucket all-reduce" if engine.overlap else " serial all-reduce")),
                        "optimizer": f"{args.optimizer} tile {args.tile}, lr {ns.lr}, wd {WD}, cuda graph",
                        "forward_backward": "eager" if args.no_step_graph else "micro-batch CUDA graphs (public Trainer option)",
                        "activation_checkpointing": checkpointing,

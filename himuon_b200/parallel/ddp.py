@@ -2,12 +2,13 @@
 
 Every trainable parameter's ``.grad`` is a view into one flat region of the symmetric heap (per dtype), so the
 weight-gradient GEMMs accumulate straight into the communication buffer and no copy precedes the collective.
-Accumulation micro-steps do no communication (the reference's ``no_sync()``, ``train_ddp.py:158-161``).  On the
-synchronising micro-step the reduction overlaps the backward pass the way the DDP reducer's buckets do
-(``train_ddp.py:90``): the decoder layers' matrices are laid out layer by layer, a bucket is a run of consecutive
-layers, and as soon as the backward pass has left a bucket's first layer its all-reduce starts on a side stream with
-a small grid, beside the remaining backward GEMMs.  What is left when backward ends (embeddings, norm weights, whose
-gradients are folded in at the very end) is reduced by one more launch.
+Accumulation micro-steps do no communication (the reference's ``no_sync()``, ``train_ddp.py:158-161``).  After the
+synchronising micro-step each dtype region is reduced by one full-grid launch (the default), or, with
+``overlap=True``, the reduction overlaps the backward pass the way the DDP reducer's buckets do (``train_ddp.py:90``):
+the decoder layers' matrices are laid out layer by layer, a bucket is a run of consecutive layers, and as soon as the
+backward pass has left a bucket's first layer its all-reduce starts on a side stream with a small grid, beside the
+remaining backward GEMMs; what is left when backward ends (embeddings, norm weights, whose gradients are folded in
+at the very end) is reduced by one more launch.
 Replaces ``torch.nn.parallel.DistributedDataParallel`` and its bucketed NCCL all-reduce.
 """
 
@@ -27,8 +28,12 @@ _LAYER_RE = re.compile(r"(?:^|\.)layers\.(\d+)\.")
 
 class DataParallelEngine:
     def __init__(self, model: torch.nn.Module, timeout_s: float = 120.0, broadcast_params: bool = True,
-                 overlap: bool = True, bucket_layers: int = 4, comm_blocks: int = 16, nvls: bool = False):
-        """``overlap``: start each bucket's all-reduce from inside the backward pass (side stream);
+                 overlap: bool = False, bucket_layers: int = 4, comm_blocks: int = 16, nvls: bool = False):
+        """``overlap``: start each bucket's all-reduce from inside the backward pass (side stream) instead of one
+        full-grid launch per region after it.  Off by default: on B200 / NVLink 5 the single launch measured faster at
+        every size tried (Qwen3-0.6B, 1.19 GB of gradients: equal on 2 GPUs, 1.4 % faster on 4, 1.8 % on 8), because
+        the all-reduce takes 3 ms at full grid while the small-grid bucket launches slow the power-limited backward
+        GEMMs by as much as they hide;
         ``bucket_layers``: decoder layers per bucket; ``comm_blocks``: grid cap of the overlapped all-reduce launches
         (they share the SMs with the backward GEMMs); ``nvls``: bind the gradient heap to an NVLink multicast object
         and reduce / broadcast through the switch (``multimem``) instead of peer loads and stores."""

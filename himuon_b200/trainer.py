@@ -66,6 +66,10 @@ def build_arg_parser(mode: str) -> argparse.ArgumentParser:
     p.add_argument("--dtype", type=str, default=None, choices=["bf16", "fp32"],
                    help="parameter dtype (default: bf16 on CUDA, fp32 on CPU)")
     p.add_argument("--device", type=str, default=None)
+    if mode == "ddp":
+        p.add_argument("--ddp-overlap", dest="ddp_overlap", action="store_true",
+                       help="start per-bucket all-reduces from inside the last backward pass (side stream) instead of one "
+                            "full-grid all-reduce after it")
     if mode in ("ddp", "fsdp"):
         p.add_argument("--nvls", action="store_true",
                        help="bind the gradient heap to an NVLink multicast object and reduce through the switch (multimem)")
@@ -386,7 +390,8 @@ def run_training(args, mode: str) -> dict:
     engine, banks = None, None
     if mode == "ddp":
         from .parallel.ddp import DataParallelEngine
-        engine = DataParallelEngine(model, nvls=bool(getattr(args, "nvls", False)))
+        engine = DataParallelEngine(model, nvls=bool(getattr(args, "nvls", False)),
+                                    overlap=bool(getattr(args, "ddp_overlap", False)))
     elif mode == "fsdp":
         from .parallel.fsdp import ShardedEngine
         # Banks (whole matrices sharded on the layer axis) serve every optimizer that updates a stacked (n, H, W)

@@ -59,8 +59,8 @@ def scenario_train(mode, optimizer_name):
                 assert b["grads"] <= (1.0 / world + 1.0 / groups) * b["banks_padded"] + 1, b
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
-        engine = DataParallelEngine(model, bucket_layers=2)
-        assert engine.overlap == (world > 1) and engine.n_buckets == -(-layers // 2)
+        engine = DataParallelEngine(model, bucket_layers=2, overlap="overlap" in opts)
+        assert engine.overlap == (world > 1 and "overlap" in opts) and engine.n_buckets == -(-layers // 2)
     ns = argparse.Namespace(lr=0.02, weight_decay=0.1, tile_size=16, cuda_graph=False)
     opt = get_optimizer(optimizer_name, model, ns)
     if mode == "fsdp":
@@ -70,7 +70,7 @@ def scenario_train(mode, optimizer_name):
     all_losses = [None] * world
     dist.all_gather_object(all_losses, losses)
     sd = engine.full_state_dict() if mode == "fsdp" else {k: v.detach().clone() for k, v in model.state_dict().items()}
-    if mode == "ddp" and world > 1:     # every optimizer step reduced all buckets from inside its last backward pass
+    if mode == "ddp" and engine.overlap:     # every optimizer step reduced all buckets from inside its last backward pass
         assert engine.overlapped_launches == 3 * engine.n_buckets, engine.overlapped_launches
     if mode == "fsdp" and opts and world > 1:
         groups = engine.n_groups

@@ -120,9 +120,9 @@ def scenario_train(mode, optimizer_name, device):
     else:
         from himuon_b200.parallel.ddp import DataParallelEngine
         # 5 layers in buckets of 2: three buckets, the last one short
-        engine = DataParallelEngine(model, timeout_s=30.0, bucket_layers=2, overlap="serial" not in opts,
+        engine = DataParallelEngine(model, timeout_s=30.0, bucket_layers=2, overlap="overlap" in opts,
                                     nvls="nvls" in opts)
-        assert engine.overlap == (world > 1 and "serial" not in opts)
+        assert engine.overlap == (world > 1 and "overlap" in opts)
     lr = 1e-3 if optimizer_name == "adamw" else 0.02
     ns = argparse.Namespace(lr=lr, weight_decay=0.1, tile_size=128, cuda_graph=True, cuda_graph_warmup=1)
     opt = get_optimizer(optimizer_name, model, ns)
